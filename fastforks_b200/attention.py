@@ -1,0 +1,223 @@
+"""The attention operator of the kernels backend: `softmax(scale * q k^T + bias) v`, head dim 64, fp16 / bf16.
+
+Host side of the path the reference runs through `Flash64._run` (`src/fastforks/kernels/fastbb/__init__.py:124-136`)
+and through `F.scaled_dot_product_attention` in its kernels-mode block forwards
+(`src/fastforks/_optimize/transformer.py:286-289`, `src/fastforks/promptable_segmentation/models/sam/fused.py:80-86`):
+check the launch contract, allocate the output with torch, describe the (possibly strided) views to the C-ABI
+library and launch on torch's current stream. Nothing here computes attention: without the CUDA library the call
+raises `KernelUnavailableError`.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import TYPE_CHECKING
+
+import torch
+
+from . import _lib
+
+if TYPE_CHECKING:
+    from collections.abc import Sequence
+
+HEAD_DIM = 64
+_DTYPES = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+_BIAS_DTYPES = {**_DTYPES, torch.float32: _lib.F32}
+_SCHEDULES = {"auto": _lib.SCHED_AUTO, "long": _lib.SCHED_LONG, "short": _lib.SCHED_SHORT}
+LAYOUTS = ("bhnd", "bnhd")
+
+
+def _strides(t: torch.Tensor, layout: str) -> tuple[int, int, int]:
+    """(batch, token, head) element strides of a 4-D view in `layout`."""
+    if layout == "bhnd":
+        return t.stride(0), t.stride(2), t.stride(1)
+    return t.stride(0), t.stride(1), t.stride(2)
+
+
+def _sizes(t: torch.Tensor, layout: str) -> tuple[int, int, int]:
+    """(batch, tokens, heads) of a 4-D view in `layout`."""
+    if layout == "bhnd":
+        return t.shape[0], t.shape[2], t.shape[1]
+    return t.shape[0], t.shape[1], t.shape[2]
+
+
+def check_operands(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layout: str = "bhnd", out: torch.Tensor | None = None
+) -> None:
+    """Check the launch contract, before anything is launched (the reference's `check_flash64`,
+    `src/fastforks/kernels/fastbb/__init__.py:51-67`, widened to bf16 and to both layouts).
+
+    Raises:
+        ValueError: A dtype, head dim, shape, device, stride or autograd state the kernels cannot take.
+    """
+    if layout not in LAYOUTS:
+        msg = f"attention: layout {layout!r}: expected one of {LAYOUTS}"
+        raise ValueError(msg)
+    ts = (("q", q), ("k", k), ("v", v)) + ((("out", out),) if out is not None else ())
+    for name, t in ts:
+        if (
+            t.dtype not in _DTYPES
+            or not t.is_cuda
+            or t.dim() != 4  # noqa: PLR2004
+            or t.shape[-1] != HEAD_DIM
+            or t.stride(-1) != 1
+        ):
+            msg = (
+                f"attention: {name} must be a float16 / bfloat16 CUDA 4-D tensor with head dim {HEAD_DIM} and unit "
+                f"last stride, got {tuple(t.shape)} {t.dtype} {t.device} strides {t.stride()}"
+            )
+            raise ValueError(msg)
+        if t.dtype != q.dtype or t.device != q.device:
+            msg = f"attention: {name} is {t.dtype} on {t.device}, q is {q.dtype} on {q.device}"
+            raise ValueError(msg)
+        if name != "out" and t.requires_grad and torch.is_grad_enabled():
+            msg = f"attention: {name} requires grad; the kernels backend is inference-only (use torch.no_grad())"
+            raise ValueError(msg)
+    if k.shape != v.shape:
+        msg = f"attention: k and v shapes differ: {tuple(k.shape)} vs {tuple(v.shape)}"
+        raise ValueError(msg)
+    bq, _, hq = _sizes(q, layout)
+    bk, _, hk = _sizes(k, layout)
+    if (bq, hq) != (bk, hk):
+        msg = f"attention: q {tuple(q.shape)} and k / v {tuple(k.shape)} differ in batch or heads"
+        raise ValueError(msg)
+    if out is not None and out.shape != q.shape:
+        msg = f"attention: out shape {tuple(out.shape)} differs from q {tuple(q.shape)}"
+        raise ValueError(msg)
+    if q.numel() == 0 or k.numel() == 0:
+        msg = f"attention: empty operand: q {tuple(q.shape)}, k {tuple(k.shape)}"
+        raise ValueError(msg)
+
+
+def _bias_view(name: str, t: torch.Tensor, shape: Sequence[int], q: torch.Tensor) -> torch.Tensor:
+    """`t` as a view broadcast to 4-D `shape` with unit last stride (a copy only if its last stride is not 1)."""
+    if t.dtype not in _BIAS_DTYPES or t.device != q.device:
+        msg = f"attention: {name} must be float16 / bfloat16 / float32 on {q.device}, got {t.dtype} on {t.device}"
+        raise ValueError(msg)
+    if t.dim() > 4:  # noqa: PLR2004
+        msg = f"attention: {name} has {t.dim()} dims, at most 4 are allowed"
+        raise ValueError(msg)
+    while t.dim() < 4:  # noqa: PLR2004
+        t = t.unsqueeze(0)
+    if t.shape[-1] != shape[-1] or t.shape[-2] != shape[-2]:
+        if t.shape[-1] not in (1, shape[-1]) or t.shape[-2] not in (1, shape[-2]):
+            msg = f"attention: {name} of shape {tuple(t.shape)} does not broadcast to {tuple(shape)}"
+            raise ValueError(msg)
+        t = t.expand(t.shape[0], t.shape[1], shape[-2], shape[-1]).contiguous()
+    if t.stride(-1) != 1:
+        t = t.contiguous()
+    try:
+        return t.expand(*shape)
+    except RuntimeError as e:
+        msg = f"attention: {name} of shape {tuple(t.shape)} does not broadcast to {tuple(shape)}"
+        raise ValueError(msg) from e
+
+
+def attention(  # noqa: PLR0913
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    *,
+    scale: float | None = None,
+    bias: torch.Tensor | None = None,
+    rel: tuple[torch.Tensor, torch.Tensor] | None = None,
+    layout: str = "bhnd",
+    out: torch.Tensor | None = None,
+    schedule: str = "auto",
+) -> torch.Tensor:
+    """`softmax(scale * q k^T + bias) v` on the B200 kernels; q, k, v are views, nothing is copied.
+
+    Args:
+        q: fp16 / bf16 CUDA `[B, heads, N, 64]` (`layout="bhnd"`, the SDPA layout) or `[B, N, heads, 64]`
+            (`layout="bnhd"`, views of a packed qkv tensor); unit last stride, other strides multiples of 8.
+        k: Same layout as q, `[.., Nk, ..]`.
+        v: Same shape as k.
+        scale: Softmax scale; default `64 ** -0.5` as in SDPA and the reference's modules.
+        bias: Additive float bias broadcastable to `[B, heads, N, Nk]` (an SDPA float `attn_mask`).
+        rel: SAM's decomposed relative-position term `(rel_h [B, heads, N, kh], rel_w [B, heads, N, kw])` with
+            `kh * kw == Nk`: `bias[i, j] = rel_h[i, j // kw] + rel_w[i, j % kw]`
+            (`src/fastforks/promptable_segmentation/models/sam/net/image_encoder.py:326-362`), never materialised.
+        layout: `"bhnd"` or `"bnhd"`.
+        out: Optional output view of q's shape and dtype.
+        schedule: `"auto"`, `"long"` or `"short"` tile schedule.
+
+    Returns:
+        A tensor of q's shape. Without `out` its memory is `[B, N, heads, 64]`-contiguous in both layouts, so the
+        `transpose(1, 2).reshape(B, N, C)` that follows SDPA in the reference's block forwards is a free view.
+
+    Raises:
+        ValueError: Operands outside the launch contract (checked before the launch).
+        KernelUnavailableError: The CUDA library is not built or does not load.
+        RuntimeError: A CUDA error at launch.
+    """
+    check_operands(q, k, v, layout, out)
+    if schedule not in _SCHEDULES:
+        msg = f"attention: schedule {schedule!r}: expected one of {tuple(_SCHEDULES)}"
+        raise ValueError(msg)
+    if bias is not None and rel is not None:
+        msg = "attention: bias and rel are mutually exclusive"
+        raise ValueError(msg)
+    lib = _lib.library()
+    b, n, h = _sizes(q, layout)
+    _, nk, _ = _sizes(k, layout)
+    if out is None:
+        o = torch.empty((b, n, h, HEAD_DIM), device=q.device, dtype=q.dtype)
+        out = o.transpose(1, 2) if layout == "bhnd" else o
+
+    a = _lib.B200AttnArgs()
+    a.struct_size = ctypes.sizeof(_lib.B200AttnArgs)
+    a.dtype = _DTYPES[q.dtype]
+    a.q, a.k, a.v, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    a.q_stride[:] = _strides(q, layout)
+    a.k_stride[:] = _strides(k, layout)
+    a.v_stride[:] = _strides(v, layout)
+    a.o_stride[:] = _strides(out, layout)
+    a.batch, a.heads, a.q_tokens, a.kv_tokens, a.head_dim = b, h, n, nk, HEAD_DIM
+    a.scale = float(HEAD_DIM**-0.5 if scale is None else scale)
+    a.schedule = _SCHEDULES[schedule]
+    keep = []  # views that must outlive the launch call
+    if bias is not None:
+        if bias.dtype == torch.bool:  # SDPA: True = takes part in attention
+            bias = torch.zeros_like(bias, dtype=q.dtype).masked_fill_(~bias, float("-inf"))
+        bv = _bias_view("bias", bias, (b, h, n, nk), q)
+        keep.append(bv)
+        a.bias, a.bias_dtype = bv.data_ptr(), _BIAS_DTYPES[bv.dtype]
+        a.bias_stride[:] = bv.stride()[:3]
+    if rel is not None:
+        rel_h, rel_w = rel
+        if rel_h.dim() != 4 or rel_w.dim() != 4 or rel_h.dtype != rel_w.dtype:  # noqa: PLR2004
+            msg = "attention: rel_h and rel_w must be 4-D tensors of one dtype"
+            raise ValueError(msg)
+        kh, kw = rel_h.shape[-1], rel_w.shape[-1]
+        if kh * kw != nk:
+            msg = f"attention: rel_h / rel_w widths {kh} * {kw} must equal the number of keys {nk}"
+            raise ValueError(msg)
+        rh = _bias_view("rel_h", rel_h, (b, h, n, kh), q)
+        rw = _bias_view("rel_w", rel_w, (b, h, n, kw), q)
+        keep += [rh, rw]
+        a.rel_h, a.rel_w, a.rel_dtype, a.rel_kh, a.rel_kw = rh.data_ptr(), rw.data_ptr(), _BIAS_DTYPES[rh.dtype], kh, kw
+        a.rel_h_stride[:] = rh.stride()[:3]
+        a.rel_w_stride[:] = rw.stride()[:3]
+
+    index = q.device.index if q.device.index is not None else torch.cuda.current_device()
+    if index != torch.cuda.current_device():
+        with torch.cuda.device(index):
+            code = lib.b200_attn_fwd(ctypes.byref(a), torch._C._cuda_getCurrentRawStream(index))  # noqa: SLF001
+    else:
+        code = lib.b200_attn_fwd(ctypes.byref(a), torch._C._cuda_getCurrentRawStream(index))  # noqa: SLF001
+    _lib.raise_for_code(code, "attention")
+    for t in keep:  # the launch is asynchronous: tie temporaries to the stream
+        t.record_stream(torch.cuda.current_stream(q.device))
+    return out
+
+
+def device_status(device: torch.device | int | None = None) -> int:
+    """Read and clear the device-side error word (synchronises the device). 0 = every kernel ran to the end.
+
+    A non-zero value means a kernel gave up a bounded wait and returned early; its output is invalid.
+    """
+    word = ctypes.c_uint32(0)
+    with torch.cuda.device(device):
+        code = _lib.library().b200_attn_status(ctypes.byref(word))
+    _lib.raise_for_code(code, "attention status")
+    return int(word.value)

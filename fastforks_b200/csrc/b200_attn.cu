@@ -1,0 +1,256 @@
+// C ABI of libb200attn.so: argument checks, TMA descriptor construction and kernel launches.
+// Declarations and the reference interfaces they replace are in include/b200_attn.h.
+#include "../../include/b200_attn.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "attn_fwd_sm100.cuh"
+
+namespace {
+
+using namespace b200;
+
+// Role bits of waits that gave up; one word per device that loaded the library.
+__device__ uint32_t g_status_word;
+
+thread_local char tl_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tl_error, sizeof(tl_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(B200_ATTN_CUDA_ERROR_BASE + static_cast<int>(e), "%s: %s", what, cudaGetErrorString(e));
+}
+
+// cuTensorMapEncodeTiled, fetched through the runtime so that the library needs no link-time libcuda.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      sym = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+// A [batch, tokens, heads, 64] view with arbitrary (16-byte multiple) strides as a 4-D tensor map whose
+// box is one 128-row x 64-column tile of one head, written to shared memory with the 128-byte swizzle.
+int make_tile_map(CUtensorMap* map, const void* base, uint32_t dtype, int batch, int heads, int tokens,
+                  const int64_t stride[3], const char* name) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr) return fail(B200_ATTN_CUDA_ERROR_BASE, "cuTensorMapEncodeTiled is not available from this driver");
+  // A dimension of extent 1 is only ever addressed at coordinate 0: any legal stride will do.
+  const int64_t sb = batch > 1 ? stride[0] : kHeadDim;
+  const int64_t sn = tokens > 1 ? stride[1] : kHeadDim;
+  const int64_t sh = heads > 1 ? stride[2] : kHeadDim;
+  cuuint64_t dims[4] = {kHeadDim, static_cast<cuuint64_t>(tokens), static_cast<cuuint64_t>(heads),
+                        static_cast<cuuint64_t>(batch)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(sn) * 2, static_cast<cuuint64_t>(sh) * 2,
+                           static_cast<cuuint64_t>(sb) * 2};
+  cuuint32_t box[4] = {kHeadDim, kTileRows, 1, 1};
+  cuuint32_t elem[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, dtype == B200_ATTN_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                   const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(B200_ATTN_UNSUPPORTED, "tensor map for %s rejected by the driver (CUresult %d)", name, static_cast<int>(r));
+  return B200_ATTN_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int check_view(const char* name, const void* ptr, const int64_t s[3], int batch, int heads, int tokens) {
+  if (ptr == nullptr) return fail(B200_ATTN_BAD_CONFIG, "%s is NULL", name);
+  if (!aligned16(ptr)) return fail(B200_ATTN_UNSUPPORTED, "%s is not 16-byte aligned", name);
+  const int ext[3] = {batch, tokens, heads};
+  const char* dim[3] = {"batch", "token", "head"};
+  for (int i = 0; i < 3; ++i) {
+    if (ext[i] <= 1) continue;
+    if (s[i] <= 0 || s[i] % 8 != 0)
+      return fail(B200_ATTN_UNSUPPORTED, "%s %s stride %lld must be a positive multiple of 8 elements", name, dim[i],
+                  static_cast<long long>(s[i]));
+    if (s[i] >= (int64_t(1) << 38))
+      return fail(B200_ATTN_UNSUPPORTED, "%s %s stride %lld is too large for a tensor map", name, dim[i],
+                  static_cast<long long>(s[i]));
+  }
+  return B200_ATTN_OK;
+}
+
+int bias_elem_size(uint32_t dtype) { return dtype == B200_ATTN_F32 ? 4 : 2; }
+
+// The argument checks shared by b200_attn_fwd and b200_attn_query. Sets *bias_mode and *schedule.
+int validate(const B200AttnArgs* a, int* bias_mode, int* schedule) {
+  if (a == nullptr) return fail(B200_ATTN_BAD_CONFIG, "args is NULL");
+  if (a->struct_size != sizeof(B200AttnArgs))
+    return fail(B200_ATTN_BAD_CONFIG, "struct_size %u does not match this library's B200AttnArgs (%zu bytes)",
+                a->struct_size, sizeof(B200AttnArgs));
+  if (a->dtype != B200_ATTN_F16 && a->dtype != B200_ATTN_BF16)
+    return fail(B200_ATTN_BAD_CONFIG, "dtype %u: q, k, v, o must be fp16 (0) or bf16 (1)", a->dtype);
+  if (a->head_dim != kHeadDim)
+    return fail(B200_ATTN_UNSUPPORTED, "head_dim %d: only head dim 64 is built", a->head_dim);
+  if (a->batch < 1 || a->heads < 1 || a->q_tokens < 1 || a->kv_tokens < 1)
+    return fail(B200_ATTN_UNSUPPORTED, "empty problem: batch %d heads %d q_tokens %d kv_tokens %d", a->batch, a->heads,
+                a->q_tokens, a->kv_tokens);
+  if (!(a->scale > 0.f) || !std::isfinite(a->scale))
+    return fail(B200_ATTN_UNSUPPORTED, "scale %g must be finite and positive", static_cast<double>(a->scale));
+  int rc;
+  if ((rc = check_view("q", a->q, a->q_stride, a->batch, a->heads, a->q_tokens))) return rc;
+  if ((rc = check_view("k", a->k, a->k_stride, a->batch, a->heads, a->kv_tokens))) return rc;
+  if ((rc = check_view("v", a->v, a->v_stride, a->batch, a->heads, a->kv_tokens))) return rc;
+  if ((rc = check_view("o", a->o, a->o_stride, a->batch, a->heads, a->q_tokens))) return rc;
+  const int64_t items = (static_cast<int64_t>(a->q_tokens) + 2 * kTileRows - 1) / (2 * kTileRows);
+  if (items * a->batch * a->heads > 0x7fffffffLL)
+    return fail(B200_ATTN_UNSUPPORTED, "problem too large for one launch (%lld CTAs)",
+                static_cast<long long>(items * a->batch * a->heads));
+
+  *bias_mode = kBiasNone;
+  const bool has_rel = a->rel_h != nullptr || a->rel_w != nullptr;
+  if (a->bias != nullptr && has_rel)
+    return fail(B200_ATTN_BAD_CONFIG, "bias and rel_h / rel_w are mutually exclusive");
+  if (a->bias != nullptr) {
+    if (a->bias_dtype > B200_ATTN_F32) return fail(B200_ATTN_BAD_CONFIG, "bias_dtype %u unknown", a->bias_dtype);
+    if (reinterpret_cast<uintptr_t>(a->bias) % bias_elem_size(a->bias_dtype) != 0)
+      return fail(B200_ATTN_UNSUPPORTED, "bias pointer is not aligned to its element size");
+    for (int i = 0; i < 3; ++i)
+      if (a->bias_stride[i] < 0) return fail(B200_ATTN_UNSUPPORTED, "bias strides must be non-negative");
+    *bias_mode = kBiasDense;
+  } else if (has_rel) {
+    if (a->rel_h == nullptr || a->rel_w == nullptr)
+      return fail(B200_ATTN_BAD_CONFIG, "rel_h and rel_w must be given together");
+    if (a->rel_dtype > B200_ATTN_F32) return fail(B200_ATTN_BAD_CONFIG, "rel_dtype %u unknown", a->rel_dtype);
+    if (a->rel_kh < 1 || a->rel_kw < 1 || static_cast<int64_t>(a->rel_kh) * a->rel_kw != a->kv_tokens)
+      return fail(B200_ATTN_UNSUPPORTED, "rel_kh * rel_kw (%d * %d) must equal kv_tokens %d", a->rel_kh, a->rel_kw,
+                  a->kv_tokens);
+    const int es = bias_elem_size(a->rel_dtype);
+    if (reinterpret_cast<uintptr_t>(a->rel_h) % es != 0 || reinterpret_cast<uintptr_t>(a->rel_w) % es != 0)
+      return fail(B200_ATTN_UNSUPPORTED, "rel_h / rel_w pointers are not aligned to their element size");
+    for (int i = 0; i < 3; ++i)
+      if (a->rel_h_stride[i] < 0 || a->rel_w_stride[i] < 0)
+        return fail(B200_ATTN_UNSUPPORTED, "rel_h / rel_w strides must be non-negative");
+    *bias_mode = kBiasDecomposed;
+  }
+
+  if (a->schedule < B200_ATTN_SCHED_AUTO || a->schedule > B200_ATTN_SCHED_SHORT)
+    return fail(B200_ATTN_BAD_CONFIG, "schedule %d unknown", a->schedule);
+  *schedule = B200_ATTN_SCHED_LONG;
+  tl_error[0] = '\0';
+  return B200_ATTN_OK;
+}
+
+constexpr int kStages = 4;
+
+template <typename T, int BIAS>
+int launch(const B200AttnArgs* a, const AttnParams& prm, const CUtensorMap& mq, const CUtensorMap& mk,
+           const CUtensorMap& mv, cudaStream_t stream) {
+  auto kernel = attn_fwd_kernel<T, BIAS, kStages, false>;
+  constexpr int smem = static_cast<int>(sizeof(AttnSmem<kStages, false>)) + 1024;
+  // The opt-in is per device and per kernel; setting it again is cheap and keeps this path stateless.
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(shared memory)");
+  const unsigned grid = static_cast<unsigned>(prm.items_per_head) * a->batch * a->heads;
+  kernel<<<grid, kThreads, smem, stream>>>(mq, mk, mv, prm);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "attention kernel launch");
+  return B200_ATTN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200_attn_query(const B200AttnArgs* args, int32_t* schedule) {
+  int bias_mode = 0, sched = 0;
+  const int rc = validate(args, &bias_mode, &sched);
+  if (rc == B200_ATTN_OK && schedule != nullptr) *schedule = sched;
+  return rc;
+}
+
+int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
+  int bias_mode = 0, sched = 0;
+  int rc = validate(a, &bias_mode, &sched);
+  if (rc != B200_ATTN_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+
+  CUtensorMap mq, mk, mv;
+  if ((rc = make_tile_map(&mq, a->q, a->dtype, a->batch, a->heads, a->q_tokens, a->q_stride, "q"))) return rc;
+  if ((rc = make_tile_map(&mk, a->k, a->dtype, a->batch, a->heads, a->kv_tokens, a->k_stride, "k"))) return rc;
+  if ((rc = make_tile_map(&mv, a->v, a->dtype, a->batch, a->heads, a->kv_tokens, a->v_stride, "v"))) return rc;
+
+  AttnParams prm;
+  std::memset(&prm, 0, sizeof(prm));
+  prm.batch = a->batch;
+  prm.heads = a->heads;
+  prm.q_tokens = a->q_tokens;
+  prm.kv_tokens = a->kv_tokens;
+  prm.items_per_head = (a->q_tokens + 2 * kTileRows - 1) / (2 * kTileRows);
+  prm.kv_tiles = (a->kv_tokens + kTileRows - 1) / kTileRows;
+  prm.scale_log2 = a->scale * kLog2e;
+  prm.o = a->o;
+  prm.o_sb = a->o_stride[0];
+  prm.o_sn = a->o_stride[1];
+  prm.o_sh = a->o_stride[2];
+  if (bias_mode == kBiasDense) {
+    prm.bias = BiasView{a->bias, a->bias_stride[0], a->bias_stride[1], a->bias_stride[2],
+                        static_cast<int>(a->bias_dtype)};
+  } else if (bias_mode == kBiasDecomposed) {
+    prm.bias = BiasView{a->rel_h, a->rel_h_stride[0], a->rel_h_stride[1], a->rel_h_stride[2],
+                        static_cast<int>(a->rel_dtype)};
+    prm.bias2 = BiasView{a->rel_w, a->rel_w_stride[0], a->rel_w_stride[1], a->rel_w_stride[2],
+                         static_cast<int>(a->rel_dtype)};
+    prm.rel_kw = a->rel_kw;
+  }
+  cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&prm.status), g_status_word);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(status word)");
+
+  const bool f16 = a->dtype == B200_ATTN_F16;
+  switch (bias_mode) {
+    case kBiasNone:
+      return f16 ? launch<__half, kBiasNone>(a, prm, mq, mk, mv, stream)
+                 : launch<__nv_bfloat16, kBiasNone>(a, prm, mq, mk, mv, stream);
+    case kBiasDense:
+      return f16 ? launch<__half, kBiasDense>(a, prm, mq, mk, mv, stream)
+                 : launch<__nv_bfloat16, kBiasDense>(a, prm, mq, mk, mv, stream);
+    default:
+      return f16 ? launch<__half, kBiasDecomposed>(a, prm, mq, mk, mv, stream)
+                 : launch<__nv_bfloat16, kBiasDecomposed>(a, prm, mq, mk, mv, stream);
+  }
+}
+
+int b200_attn_status(uint32_t* status) {
+  if (status == nullptr) return fail(B200_ATTN_BAD_CONFIG, "status is NULL");
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceSynchronize");
+  uint32_t word = 0, zero = 0;
+  e = cudaMemcpyFromSymbol(&word, g_status_word, sizeof(word));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyFromSymbol(status word)");
+  if (word != 0) {
+    e = cudaMemcpyToSymbol(g_status_word, &zero, sizeof(zero));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyToSymbol(status word)");
+  }
+  *status = word;
+  return B200_ATTN_OK;
+}
+
+const char* b200_attn_last_error(void) { return tl_error; }
+
+const char* b200_attn_version(void) { return "b200attn 0.1 (sm_100a, tcgen05 + TMA)"; }
+
+}  // extern "C"

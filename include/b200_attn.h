@@ -1,0 +1,132 @@
+/*
+ * b200_attn.h - C ABI of the B200 (sm_100a) attention-forward library `libb200attn.so`.
+ *
+ * The library computes  O = softmax(scale * Q K^T + bias) V  for head dim 64, fp16 or bf16, non-causal,
+ * with fp32 accumulation, on hand-written tcgen05 / TMA kernels.  It is the replacement for the two
+ * forms the reference's kernels backend uses for this operation:
+ *
+ *   - the `flash64_r{1,2}_{hh,fh,ff}` kernels (src/fastforks/kernels/fastbb/fastbb_kernels.cu:58-307)
+ *     launched by `Flash64._run` (src/fastforks/kernels/fastbb/__init__.py:124-136) on strided
+ *     `[B, N, heads, 64]` views of a packed qkv tensor;
+ *   - the `F.scaled_dot_product_attention(q, k, v, attn_mask=..., scale=...)` calls on `[B, heads, N, 64]`
+ *     views in the kernels-mode block forwards (src/fastforks/_optimize/transformer.py:286-289, 476-479)
+ *     and in the SAM encoder, where the decomposed relative-position bias is folded into widened q / k
+ *     (src/fastforks/promptable_segmentation/models/sam/fast.py:92-113, fused.py:80-86).
+ *
+ * Conventions follow the reference's `shared`-kind kernel libraries
+ * (src/fastforks/_core/kernels.py:481-494, src/fastforks/kernels/dpt_fused/dpt_fused.cu:17-18):
+ * plain pointers and sizes, the caller owns every buffer, the launch goes to the stream the caller
+ * passes and never synchronises, the return value is a status code.
+ *
+ * All pointers are device pointers.  Strides are in ELEMENTS of the tensor's own dtype.
+ */
+#ifndef B200_ATTN_H_
+#define B200_ATTN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Return codes (the reference's convention: 0 = ran, 1 = geometry / alignment unsupported,
+ * -1 = unknown configuration, anything else = CUDA error). CUDA errors are 1000 + cudaError_t. */
+#define B200_ATTN_OK 0
+#define B200_ATTN_UNSUPPORTED 1
+#define B200_ATTN_BAD_CONFIG (-1)
+#define B200_ATTN_CUDA_ERROR_BASE 1000
+
+/* Element types. */
+#define B200_ATTN_F16 0
+#define B200_ATTN_BF16 1
+#define B200_ATTN_F32 2 /* bias tensors only */
+
+/* Tile schedules. AUTO picks by sequence length. */
+#define B200_ATTN_SCHED_AUTO 0
+#define B200_ATTN_SCHED_LONG 1  /* one or two 128-row query tiles of one head per CTA, K/V streamed */
+#define B200_ATTN_SCHED_SHORT 2 /* persistent CTAs walking many (batch, head) pairs, next head prefetched */
+
+/*
+ * One attention call.  Element (b, n, h, d) of q lives at q + b*q_stride[0] + n*q_stride[1] + h*q_stride[2] + d
+ * (same for k, v, o), exactly the addressing of the reference kernel (fastbb_kernels.cu:52-54), so both the
+ * `[B, N, heads, 64]` views of packed qkv and the `[B, heads, N, 64]` SDPA layout are described without a copy.
+ * Requirements: head_dim == 64, unit stride along d, base pointers 16-byte aligned, strides multiples of 8.
+ */
+typedef struct B200AttnArgs {
+  uint32_t struct_size; /* sizeof(B200AttnArgs): lets the library reject a caller built against another layout */
+  uint32_t dtype;       /* B200_ATTN_F16 or B200_ATTN_BF16: type of q, k, v and o */
+
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  int64_t q_stride[3]; /* batch, token, head */
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+  int64_t o_stride[3];
+
+  int32_t batch;
+  int32_t heads;
+  int32_t q_tokens;  /* N of q and o */
+  int32_t kv_tokens; /* N of k and v (== q_tokens for self-attention) */
+  int32_t head_dim;  /* must be 64 */
+  float scale;       /* softmax scale, > 0 (the reference passes head_dim ** -0.5) */
+
+  /* Optional dense additive bias (an SDPA `attn_mask` of floating type), added to scale * q k^T.
+   * Element (b, h, i, j) at bias + b*bias_stride[0] + h*bias_stride[1] + i*bias_stride[2] + j.
+   * A stride of 0 broadcasts that dimension.  NULL = none. */
+  const void* bias;
+  uint32_t bias_dtype; /* B200_ATTN_F16 / BF16 / F32 */
+  int64_t bias_stride[3];
+
+  /* Optional decomposed bias (SAM's relative-position term, sam/net/image_encoder.py:326-362):
+   * bias(i, j) = rel_h[b, h, i, j / rel_kw] + rel_w[b, h, i, j % rel_kw], with kv_tokens == rel_kh * rel_kw.
+   * Element (b, h, i, c) at rel_h + b*rel_h_stride[0] + h*rel_h_stride[1] + i*rel_h_stride[2] + c.
+   * Both NULL = none.  Mutually exclusive with `bias`. */
+  const void* rel_h;
+  const void* rel_w;
+  uint32_t rel_dtype; /* B200_ATTN_F16 / BF16 / F32 */
+  int32_t rel_kh;
+  int32_t rel_kw;
+  int64_t rel_h_stride[3];
+  int64_t rel_w_stride[3];
+
+  int32_t schedule; /* B200_ATTN_SCHED_* */
+  int32_t reserved;
+} B200AttnArgs;
+
+/*
+ * Launches the attention forward on `stream` (a cudaStream_t / CUstream; NULL = the legacy default stream)
+ * of the current device and returns without synchronising.  Replaces the `flash64_*` launch
+ * (fastbb/__init__.py:130-135) and the SDPA call sites named above.
+ * Arguments are checked before anything is launched; a non-zero return means nothing ran.
+ */
+int b200_attn_fwd(const B200AttnArgs* args, void* stream);
+
+/*
+ * Reports whether `args` describes a call the library can run, without launching: returns the code
+ * `b200_attn_fwd` would return from its argument checks, and stores the schedule it would pick
+ * (B200_ATTN_SCHED_LONG / SHORT) in *schedule when that pointer is not NULL.  Pointers in `args` are
+ * only inspected for alignment.  Counterpart of `check_flash64` (fastbb/__init__.py:51-67).
+ */
+int b200_attn_query(const B200AttnArgs* args, int32_t* schedule);
+
+/*
+ * Reads and clears the device-side error word of the current device (synchronises that device).
+ * 0 = every wait inside the kernels completed.  Non-zero: a kernel gave up a bounded wait on a barrier and
+ * returned early, its output is invalid; the bits say which role (1 loader, 2 MMA issuer, 4 softmax).
+ * The reference has no counterpart: its kernels contain no waits on asynchronous units.
+ */
+int b200_attn_status(uint32_t* status);
+
+/* Human-readable reason of the calling thread's last non-zero return. Never NULL. */
+const char* b200_attn_last_error(void);
+
+/* Library version string, e.g. "b200attn 0.1 (sm_100a)". */
+const char* b200_attn_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200_ATTN_H_ */

@@ -1,0 +1,71 @@
+"""Pins the CPU oracle to the reference: every golden vector written by the reference's own modules
+(`tests/golden/make_golden.py`) must be reproduced by the numpy restatement and by the C restatement."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from oracle import attention_oracle as ao
+from oracle import c_oracle
+
+FP32_TOL = 5e-5  # fp32 round-off of two matmuls and a softmax; outputs are O(1), the peaky case O(10)
+
+
+def _bias_of(case: dict) -> tuple[np.ndarray | None, tuple | None]:
+    if "bias" not in case:
+        return None, None
+    rel = ao.decomposed_terms(case["q"], case["rel_pos_h"], case["rel_pos_w"], case["hw"])
+    return ao.decomposed_bias(*rel), rel
+
+
+def test_numpy_oracle_matches_reference_modules(golden: dict) -> None:
+    bias, _ = _bias_of(golden)
+    out = ao.attention(golden["q"], golden["k"], golden["v"], float(golden["scale"]), bias)
+    np.testing.assert_allclose(out, golden["out"], rtol=0, atol=FP32_TOL)
+
+
+def test_c_oracle_matches_reference_modules(golden: dict) -> None:
+    _, rel = _bias_of(golden)
+    out = c_oracle.attention(golden["q"], golden["k"], golden["v"], float(golden["scale"]), rel=rel, threads=2)
+    np.testing.assert_allclose(out, golden["out"], rtol=0, atol=FP32_TOL)
+
+
+@pytest.mark.parametrize("name", ["sam_window_14x14", "sam_grid_8x16"])
+def test_decomposed_bias_matches_reference_add_decomposed_rel_pos(name: str) -> None:
+    from conftest import load_golden
+
+    case = load_golden(name)
+    bias, _ = _bias_of(case)
+    np.testing.assert_allclose(bias, case["bias"], rtol=0, atol=5e-6)
+
+
+def test_c_oracle_dense_bias_equals_decomposed() -> None:
+    rng = np.random.default_rng(0)
+    q, k, v = (rng.standard_normal((1, 2, 35, 64), dtype=np.float32) for _ in range(3))
+    rel_h = rng.standard_normal((1, 2, 35, 5), dtype=np.float32)
+    rel_w = rng.standard_normal((1, 2, 35, 7), dtype=np.float32)
+    dense = ao.decomposed_bias(rel_h, rel_w)
+    a = c_oracle.attention(q, k, v, bias=dense)
+    b = c_oracle.attention(q, k, v, rel=(rel_h, rel_w))
+    c = ao.attention(q, k, v, bias=dense)
+    np.testing.assert_allclose(a, b, rtol=0, atol=1e-6)
+    np.testing.assert_allclose(a, c, rtol=0, atol=1e-5)
+
+
+def test_oracle_properties() -> None:
+    """Size-independent properties the GPU tests also use: rows of P sum to one (v = 1 -> out = 1), key
+    permutation invariance, and a huge negative bias on a key removes it."""
+    rng = np.random.default_rng(1)
+    q, k, v = (rng.standard_normal((2, 3, 50, 64), dtype=np.float32) for _ in range(3))
+    np.testing.assert_allclose(ao.attention(q, k, np.ones_like(v)), 1.0, atol=1e-5)
+    perm = rng.permutation(50)
+    np.testing.assert_allclose(ao.attention(q, k[:, :, perm], v[:, :, perm]), ao.attention(q, k, v), atol=1e-5)
+    bias = np.zeros((1, 1, 50, 50), dtype=np.float32)
+    bias[..., 10:] = -np.inf
+    np.testing.assert_allclose(ao.attention(q, k, v, bias=bias), ao.attention(q, k[:, :, :10], v[:, :, :10]), atol=1e-5)
+
+
+def test_get_rel_pos_rejects_interpolation() -> None:
+    with pytest.raises(ValueError, match="interpolation"):
+        ao.get_rel_pos(14, 14, np.zeros((5, 64), dtype=np.float32))
