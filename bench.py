@@ -1,0 +1,393 @@
+"""Benchmark of the attention hot path: attention TFLOP/s (FLOPs = 4 * B * H * N^2 * d) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One STEP is one pass of the hot path over one batch: the attention calls of all layers of one forward of the
+workload model, each layer reading its own packed qkv tensor (so consecutive launches never find their inputs in
+L2). At N GPUs every rank runs the same step on its own images (image-wise sharding, no collective on the data
+path) and the reported value is the whole-job aggregate, timed on the device as the maximum over ranks.
+
+The JSON line carries, besides the contract's keys:
+  roofline      tensor-pipe roofline of the attention kernel: achieved TFLOP/s per launch over the measured cuBLAS
+                bf16 peak (MEASURED_PEAKS.json, else the fallback 1590 TFLOP/s)
+  cpu_baseline  the reference's portable arithmetic (fp32 scaled_dot_product_attention on the host cores), timed on
+                a bounded sample on rank 0
+  e2e           the same metric through the public operator with HOST buffers: pinned-memory qkv copied to the
+                device, attention, output copied back, every step
+  regimes       the other benchmark shapes, device-timed: long-sequence TFLOP/s and short-sequence HBM GB/s
+
+`--impl reference` times the reference's own CPU implementation of the path (see `oracle/portable_attention.py`)
+on the same configuration and metric.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+HEAD_DIM = 64
+# Workload of the headline number: DINOv2 ViT-S/14 at 518x518 (N = 1 + 37 * 37), batch 8, fp16, 12 layers.
+WORKLOAD = {"name": "dinov2-vits14-518px attention", "batch": 8, "heads": 6, "tokens": 1370, "layers": 12, "dtype": "fp16"}
+# Device-timed side measurements (one layer each): the other shapes of the benchmark list.
+REGIMES = (
+    ("depth-anything-v2-l [4,16,1370,64] bf16", 4, 16, 1370, "bf16", None),
+    ("sam-vit-b global [1,12,4096,64] fp16 + rel bias", 1, 12, 4096, "fp16", (64, 64)),
+    ("dinov2-vitg14 [32,24,1370,64] bf16", 32, 24, 1370, "bf16", None),
+    ("sam-vit-b windows [25,12,196,64] fp16 + rel bias", 25, 12, 196, "fp16", (14, 14)),
+    ("vit-b16 [256,12,197,64] fp16", 256, 12, 197, "fp16", None),
+    ("vit-b16 [1,12,197,64] fp16", 1, 12, 197, "fp16", None),
+)
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0}
+
+
+def attention_flops(b: int, h: int, n: int, nk: int | None = None) -> float:
+    return 4.0 * b * h * n * (nk or n) * HEAD_DIM
+
+
+def attention_bytes(b: int, h: int, n: int, rel: tuple[int, int] | None = None) -> float:
+    """Algorithmic bytes of one call: q, k, v read once, o written once (2-byte elements), plus the bias terms."""
+    extra = 2.0 * b * h * n * (rel[0] + rel[1]) if rel else 0.0
+    return 8.0 * b * h * n * HEAD_DIM + extra
+
+
+def load_peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            data = json.loads(path.read_text())
+            return {"bf16_tflops": float(data["bf16_tflops"]), "hbm_gbs": float(data["hbm_gbs"])}, "measured"
+        except (ValueError, KeyError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    BAD = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20}
+    NOTED = {"sw_power_cap": 0x4}
+
+    def __init__(self, index: int) -> None:
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._dev = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._dev, pynvml.NVML_CLOCK_SM))
+        except Exception:  # noqa: BLE001 - NVML is optional; absence is reported as null clocks
+            self._nv = None
+
+    def _sample(self) -> None:
+        nv = self._nv
+        self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._dev, nv.NVML_CLOCK_SM)))
+        mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._dev))
+        for name, bit in {**self.BAD, **self.NOTED}.items():
+            if mask & bit:
+                self.reasons.add(name)
+
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            try:
+                self._sample()
+            except Exception:  # noqa: BLE001
+                return
+            self._stop.wait(0.002)
+
+    def __enter__(self) -> ClockSampler:
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc: object) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def cpu_reference_tflops(layers: int, threads: int, *, warm: int = 2, runs: int = 5) -> tuple[float, float, str]:
+    """The reference's portable arithmetic on the host: fp32 SDPA of `layers` layers of the workload shape.
+
+    Returns (TFLOP/s, seconds per pass, description of the sample)."""
+    import torch
+
+    from oracle.portable_attention import portable_attention
+
+    torch.set_num_threads(threads)
+    b, h, n = WORKLOAD["batch"], WORKLOAD["heads"], WORKLOAD["tokens"]
+    gen = torch.Generator().manual_seed(0)
+    qkv = [torch.randn(3, b, h, n, HEAD_DIM, generator=gen) for _ in range(layers)]
+    times = []
+    for i in range(warm + runs):
+        t0 = time.perf_counter()
+        for x in qkv:
+            portable_attention(x[0], x[1], x[2])
+        if i >= warm:
+            times.append(time.perf_counter() - t0)
+    sec = statistics.median(times)
+    sample = f"{layers} of {WORKLOAD['layers']} layers of [{b},{h},{n},{HEAD_DIM}] fp32, median of {runs} passes after {warm} warm-ups"
+    return attention_flops(b, h, n) * layers / sec / 1e12, sec, sample
+
+
+def base_line(args: argparse.Namespace) -> dict:
+    b, h, n = WORKLOAD["batch"], WORKLOAD["heads"], WORKLOAD["tokens"]
+    return {
+        "metric": "attention_tflops",
+        "unit": "TFLOP/s",
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "fp16",
+        "data": "synthetic",
+        "config": {
+            "workload": f"{WORKLOAD['name']}: {WORKLOAD['layers']} layers of q,k,v [{b},{h},{n},{HEAD_DIM}] fp16 per GPU, "
+            "strided views of packed qkv",
+            "flops_per_step_per_gpu": attention_flops(b, h, n) * WORKLOAD["layers"],
+            "l2": "each layer has its own 50 MB qkv and 17 MB output; a step touches 0.8 GB, larger than the 126 MB L2",
+            "parallelism": f"image-wise shards, {args.gpus} replica(s), no data-path collective",
+        },
+    }
+
+
+def run_reference(args: argparse.Namespace) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    layers = 2  # bounded sample of the 12-layer step; throughput is per FLOP, so the sample needs no scaling
+    for _ in range(max(0, args.warmup)):
+        cpu_reference_tflops(layers, threads, warm=0, runs=1)
+    t0 = time.perf_counter()
+    values = [cpu_reference_tflops(layers, threads, warm=0, runs=1) for _ in range(max(1, args.steps))]
+    elapsed = time.perf_counter() - t0
+    tflops = statistics.median(v[0] for v in values)
+    line = base_line(args)
+    line.update(
+        impl="reference",
+        value=tflops,
+        ms_per_step=elapsed / max(1, args.steps) * 1e3,
+        dtype="f32",
+        cpu_baseline={
+            "value": tflops,
+            "unit": "TFLOP/s",
+            "cores": threads,
+            "kind": "port",
+            "sample": f"{layers} of {WORKLOAD['layers']} layers per step: fp32 torch scaled_dot_product_attention on the host, "
+            "the call the reference's portable backend makes",
+        },
+        e2e={"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        gpu_launches=0,
+    )
+    print(json.dumps(line))
+
+
+def time_launches(fn, reps: int, torch) -> float:  # noqa: ANN001
+    """Average milliseconds of `fn()` over `reps` back-to-back calls, CUDA events on the current stream."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def run_ours(args: argparse.Namespace) -> None:  # noqa: PLR0915
+    import torch
+
+    import fastforks_b200 as ff
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world:
+        if world == 1 and args.gpus > 1:
+            msg = f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE is 1)"
+            raise SystemExit(msg)
+        args.gpus = world
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ff.resolve_mode("kernels")  # raises when the CUDA library or a B200 is missing: no fallback is timed
+
+    b, h, n, layers = WORKLOAD["batch"], WORKLOAD["heads"], WORKLOAD["tokens"], WORKLOAD["layers"]
+    gen = torch.Generator().manual_seed(1234 + rank)
+    host_qkv = [torch.randn(b, n, 3, h, HEAD_DIM, generator=gen).half().pin_memory() for _ in range(layers)]
+    dev_qkv = [x.cuda(non_blocking=True) for x in host_qkv]
+    dev_out = [torch.empty(b, n, h, HEAD_DIM, dtype=torch.float16, device="cuda") for _ in range(layers)]
+    host_out = [torch.empty(b, n, h, HEAD_DIM, dtype=torch.float16).pin_memory() for _ in range(layers)]
+    views = [x.unbind(2) for x in dev_qkv]
+    attn = ff.Flash64("hh")
+    scale = HEAD_DIM**-0.5
+    torch.cuda.synchronize()
+
+    def step() -> None:
+        for (q, k, v), o in zip(views, dev_out):
+            ff.attention(q, k, v, scale=scale, layout="bnhd", out=o)
+
+    def step_e2e() -> None:
+        for hq, ho in zip(host_qkv, host_out):
+            qkv = hq.cuda(non_blocking=True)
+            q, k, v = qkv.unbind(2)
+            ho.copy_(attn(q, k, v, scale), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier() -> None:
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps: int) -> float:  # noqa: ANN001
+        """Milliseconds for `steps` calls of fn, device-timed, max over ranks."""
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    with ClockSampler(local) as clocks:
+        total_ms = timed(step, args.steps)
+        # keep the device under the same load a little longer so that the 2 ms NVML sampler sees it
+        t_end = time.perf_counter() + 0.25
+        while time.perf_counter() < t_end:
+            step()
+        torch.cuda.synchronize()
+    status = ff.device_status()
+    if status != 0:
+        msg = f"a kernel gave up a bounded wait (status {status}); the timing is void"
+        raise SystemExit(msg)
+
+    for _ in range(2):
+        step_e2e()
+    e2e_steps = max(1, min(args.steps, 10))
+    e2e_ms = timed(step_e2e, e2e_steps)
+
+    flops_step = attention_flops(b, h, n) * layers
+    value = flops_step * args.steps * world / (total_ms * 1e-3) / 1e12
+    e2e_value = flops_step * e2e_steps * world / (e2e_ms * 1e-3) / 1e12
+    per_launch_ms = total_ms / (args.steps * layers)
+    achieved = attention_flops(b, h, n) / (per_launch_ms * 1e-3) / 1e12
+    peaks, peak_kind = load_peaks()
+
+    line = base_line(args)
+    line.update(
+        value=value,
+        ms_per_step=total_ms / args.steps,
+        images_per_s=b * world * args.steps / (total_ms * 1e-3),
+        roofline={
+            "bound": "tensor",
+            "achieved": achieved,
+            "peak": peaks["bf16_tflops"],
+            "unit": "TFLOP/s",
+            "frac": achieved / peaks["bf16_tflops"],
+            "traffic": None,
+            "peak_source": f"{peak_kind} (cuBLAS bf16 burst)",
+            "kernel": "attn_fwd_kernel<half, no bias>",
+            "us_per_launch": per_launch_ms * 1e3,
+        },
+        e2e={
+            "value": e2e_value,
+            "unit": "TFLOP/s",
+            "h2d_bytes_per_step": sum(x.numel() * 2 for x in host_qkv),
+            "d2h_bytes_per_step": sum(x.numel() * 2 for x in host_out),
+        },
+        gpu_launches=args.steps * layers,
+        clocks=clocks.summary(),
+    )
+
+    if rank == 0:
+        regimes = {}
+        for name, rb, rh, rn, rdt, rel in REGIMES:
+            dt = torch.float16 if rdt == "fp16" else torch.bfloat16
+            copies = max(2, int(300e6 // attention_bytes(rb, rh, rn, rel)) + 1)  # rotate buffers: inputs larger than L2
+            copies = min(copies, 64)
+            qkvs = [torch.randn(rb, rn, 3, rh, HEAD_DIM, device="cuda").to(dt) for _ in range(copies)]
+            outs = [torch.empty(rb, rn, rh, HEAD_DIM, device="cuda", dtype=dt) for _ in range(copies)]
+            rels = None
+            if rel:
+                rels = [
+                    (torch.randn(rb, rh, rn, rel[0], device="cuda").to(dt), torch.randn(rb, rh, rn, rel[1], device="cuda").to(dt))
+                    for _ in range(copies)
+                ]
+            state = {"i": 0}
+
+            def call(qkvs=qkvs, outs=outs, rels=rels, state=state, copies=copies) -> None:  # noqa: ANN001
+                i = state["i"] = (state["i"] + 1) % copies
+                q, k, v = qkvs[i].unbind(2)
+                ff.attention(q, k, v, scale=scale, layout="bnhd", out=outs[i], rel=None if rels is None else rels[i])
+
+            ms = time_launches(call, 40, torch)
+            regimes[name] = {
+                "us_per_launch": ms * 1e3,
+                "tflops": attention_flops(rb, rh, rn) / (ms * 1e-3) / 1e12,
+                "frac_tensor_peak": attention_flops(rb, rh, rn) / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+                "hbm_gbs": attention_bytes(rb, rh, rn, rel) / (ms * 1e-3) / 1e9,
+                "frac_hbm_peak": attention_bytes(rb, rh, rn, rel) / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            }
+            del qkvs, outs, rels
+        line["regimes"] = regimes
+        line["peaks"] = {**peaks, "source": peak_kind}
+        if world == 1:
+            threads = os.cpu_count() or 1
+            tflops, sec, sample = cpu_reference_tflops(2, threads)
+            line["cpu_baseline"] = {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    args = ap.parse_args()
+    args.steps = max(1, args.steps)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

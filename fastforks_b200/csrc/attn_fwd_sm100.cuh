@@ -33,7 +33,11 @@ constexpr int kSoftmaxThreads = 256;                 // two warpgroups
 constexpr int kLoaderWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr int kThreads = 384;                        // 2 softmax warpgroups + 1 warpgroup of helpers (2 idle warps)
-constexpr int kSoftmaxRegs = 232, kHelperRegs = 48;   // per-thread register budgets after the hand-over
+constexpr int kSoftmaxRegs = 224, kHelperRegs = 48;   // per-thread register budgets after the hand-over
+constexpr int kLaunchRegs = 168;                      // what a 384-thread CTA gets per thread at launch
+// setmaxnreg.inc blocks until the CTA's pool holds the registers: the budgets must fit what the launch allocated,
+// or the second warpgroup waits for ever.
+static_assert(2 * 128 * kSoftmaxRegs + 128 * kHelperRegs <= kLaunchRegs * kThreads, "register hand-over does not balance");
 constexpr uint32_t kTmemCols = 512;                  // S0 S1 (128 each) + O0 O1 (64 each) = 384 -> next power of two
 constexpr uint32_t kTmemS = 0, kTmemO = 256;
 constexpr float kLog2e = 1.4426950408889634f;

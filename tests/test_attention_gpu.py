@@ -1,0 +1,269 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI, on a B200.
+
+Structure follows the reference's kernel fuzz test for this op (tests/test_kernel_fuzz.py:269-296): seeded random
+shapes and magnitudes, q / k / v as strided views of one packed tensor, compared with fp32 attention on the same
+fp16 / bf16-rounded operands. Here the fp32 side is the oracle (`oracle/`), pinned to the reference's own modules
+by `tests/test_oracle.py`. Tolerances (`conftest.assert_close`): max-abs <= 2e-2 and mean-abs <= 2e-3 at unit scale,
+the reference's relative 2e-2 form for other magnitudes.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import fastforks_b200 as ff
+from conftest import assert_close, load_golden
+from oracle import attention_oracle as ao
+from oracle import c_oracle
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = {"fp16": torch.float16, "bf16": torch.bfloat16}
+
+
+@pytest.fixture(autouse=True)
+def _kernels_ran_to_the_end():  # noqa: ANN202
+    """After every test the device error word must be clear: no kernel gave up a wait."""
+    yield
+    assert ff.device_status() == 0
+
+
+def packed_qkv(b: int, n: int, h: int, dtype: torch.dtype, mag: float, seed: int) -> torch.Tensor:
+    gen = torch.Generator().manual_seed(seed)
+    return (torch.randn(b, n, 3, h, 64, generator=gen) * mag).to(dtype).cuda()
+
+
+def oracle_of_packed(qkv: torch.Tensor, scale: float, **kw: object) -> np.ndarray:
+    """Oracle output `[B, N, H, 64]` from the rounded operands of a packed `[B, N, 3, H, 64]` tensor."""
+    q, k, v = (t.float().cpu().numpy() for t in qkv.permute(2, 0, 3, 1, 4))  # [B, H, N, 64]
+    big = q.shape[0] * q.shape[1] * q.shape[2] * k.shape[2] > 4_000_000
+    out = ao.attention(q, k, v, scale, **kw) if big or kw else c_oracle.attention(q, k, v, scale, threads=4)
+    return out.transpose(0, 2, 1, 3)
+
+
+def test_library_is_the_cuda_build() -> None:
+    assert ff.resolve_mode("kernels") == "kernels"
+    assert "sm_100a" in ff.version()
+
+
+@pytest.mark.parametrize("name", ["dinov2_n97", "dinov2_n257_peaky", "timm_n197"])
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_golden_vectors_of_the_reference_modules(name: str, dtype: str) -> None:
+    """Inputs captured inside the reference's DINOv2 / timm attention modules; output vs the module's own output.
+    The operands are rounded to 16 bits first, so the tolerance is the op-level one, not fp32 round-off."""
+    g = load_golden(name)
+    dt = DTYPES[dtype]
+    q, k, v = (torch.from_numpy(g[x]).to(dt).cuda() for x in "qkv")
+    got = ff.scaled_dot_product_attention(q, k, v, scale=float(g["scale"]))
+    assert_close(got.float().cpu().numpy(), g["out"], unit_scale=name != "dinov2_n257_peaky", what=f"{name} {dtype}")
+    # and exactly the oracle on the rounded operands
+    ref = ao.attention(*(t.float().cpu().numpy() for t in (q, k, v)), float(g["scale"]))
+    assert_close(got.float().cpu().numpy(), ref, unit_scale=name != "dinov2_n257_peaky", what=f"{name} {dtype} oracle")
+
+
+@pytest.mark.parametrize("name", ["sam_window_14x14", "sam_grid_8x16"])
+@pytest.mark.parametrize("form", ["decomposed", "dense"])
+def test_golden_vectors_of_the_reference_sam_attention(name: str, form: str) -> None:
+    """SAM `Attention.forward` with `add_decomposed_rel_pos`: the bias goes in as rel_h / rel_w (never materialised)
+    or as the dense `[B, H, N, N]` tensor the reference function produced."""
+    g = load_golden(name)
+    q, k, v = (torch.from_numpy(g[x]).half().cuda() for x in "qkv")
+    if form == "dense":
+        got = ff.scaled_dot_product_attention(q, k, v, attn_mask=torch.from_numpy(g["bias"]).cuda(), scale=float(g["scale"]))
+    else:
+        rel_h, rel_w = ao.decomposed_terms(g["q"], g["rel_pos_h"], g["rel_pos_w"], g["hw"])
+        rel = (torch.from_numpy(rel_h).cuda(), torch.from_numpy(rel_w).cuda())
+        got = ff.scaled_dot_product_attention(q, k, v, scale=float(g["scale"]), rel=rel)
+    assert_close(got.float().cpu().numpy(), g["out"], unit_scale=True, what=f"{name} {form}")
+
+
+@pytest.mark.parametrize("variant", ["hh", "fh", "ff"])
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_flash64_fuzz(variant: str, seed: int) -> None:
+    """The reference's fuzz of `Flash64` (tests/test_kernel_fuzz.py:284-296): b in {1,2}, n in {1, [2,63], [65,400]},
+    heads in [1,6], magnitudes 1.0 / 0.05 / 4.0, strided views of packed qkv, new contiguous output."""
+    rng = np.random.default_rng(seed)
+    attn = ff.Flash64(variant)
+    for mag in (1.0, 0.05, 4.0):
+        for n in (1, int(rng.integers(2, 64)), int(rng.integers(65, 401))):
+            b, h = int(rng.integers(1, 3)), int(rng.integers(1, 7))
+            qkv = packed_qkv(b, n, h, torch.float16, mag, seed * 1000 + n)
+            q, k, v = qkv.unbind(2)
+            got = attn(q, k, v, 0.125)
+            assert got.shape == (b, n, h, 64)
+            assert got.is_contiguous()
+            assert_close(got.float().cpu().numpy(), oracle_of_packed(qkv, 0.125), unit_scale=mag == 1.0, what=f"b{b} n{n} h{h} mag{mag}")
+
+
+@pytest.mark.parametrize("n", [1, 2, 63, 64, 65, 127, 128, 129, 196, 197, 255, 256, 257, 383, 385, 512, 513, 1370])
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_tile_boundaries(n: int, dtype: str) -> None:
+    """Sequence lengths around every tile edge of the kernel (128-row query tiles, 128-key tiles, two tiles per CTA)."""
+    qkv = packed_qkv(2, n, 3, DTYPES[dtype], 1.0, n)
+    q, k, v = qkv.unbind(2)
+    got = ff.attention(q, k, v, layout="bnhd")
+    assert_close(got.float().cpu().numpy(), oracle_of_packed(qkv, 0.125), unit_scale=True, what=f"n{n} {dtype}")
+
+
+def test_output_rows_past_the_sequence_are_untouched() -> None:
+    """Canary rows and columns around the output view must survive: the kernel writes its rows only."""
+    b, n, h = 2, 197, 3
+    qkv = packed_qkv(b, n, h, torch.float16, 1.0, 5)
+    q, k, v = qkv.unbind(2)
+    big = torch.full((b, n + 7, h + 1, 64), 77.0, dtype=torch.float16, device="cuda")
+    out = big[:, 3 : 3 + n, :h]
+    ff.attention(q, k, v, layout="bnhd", out=out)
+    assert_close(out.float().cpu().numpy(), oracle_of_packed(qkv, 0.125), unit_scale=True)
+    canary = big.clone()
+    canary[:, 3 : 3 + n, :h] = 77.0
+    assert bool((canary == 77.0).all())
+
+
+def test_sdpa_layout_and_free_transpose() -> None:
+    """`[B, H, N, 64]` permuted views as in `_vit_kernels` (src/fastforks/_optimize/transformer.py:286-289); the result's
+    `transpose(1, 2).reshape(B, N, C)` is a view."""
+    b, n, h = 2, 197, 12
+    qkv = packed_qkv(b, n, h, torch.float16, 1.0, 11)
+    q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)
+    got = ff.scaled_dot_product_attention(q, k, v)
+    assert got.shape == (b, h, n, 64)
+    flat = got.transpose(1, 2).reshape(b, n, h * 64)
+    assert flat.data_ptr() == got.data_ptr()
+    assert_close(got.transpose(1, 2).float().cpu().numpy(), oracle_of_packed(qkv, 0.125), unit_scale=True)
+
+
+def test_cross_lengths_and_scale() -> None:
+    gen = torch.Generator().manual_seed(3)
+    q = torch.randn(2, 3, 150, 64, generator=gen).half().cuda()
+    k = torch.randn(2, 3, 77, 64, generator=gen).half().cuda()
+    v = torch.randn(2, 3, 77, 64, generator=gen).half().cuda()
+    got = ff.scaled_dot_product_attention(q, k, v, scale=0.2)
+    ref = ao.attention(*(t.float().cpu().numpy() for t in (q, k, v)), 0.2)
+    assert_close(got.float().cpu().numpy(), ref, unit_scale=True)
+
+
+@pytest.mark.parametrize("bias_dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_dense_bias_broadcast_and_mask(bias_dtype: torch.dtype) -> None:
+    """A Swin-style `[1, heads, N, N]` bias broadcast over the batch (`_swin_block`, transformer.py:476-479), with
+    -inf entries acting as a mask."""
+    gen = torch.Generator().manual_seed(4)
+    b, h, n = 3, 4, 147
+    q, k, v = (torch.randn(b, h, n, 64, generator=gen).half().cuda() for _ in range(3))
+    bias = torch.randn(1, h, n, n, generator=gen).to(bias_dtype)
+    bias[..., 100:] = float("-inf")
+    got = ff.scaled_dot_product_attention(q, k, v, attn_mask=bias.cuda())
+    ref = ao.attention(*(t.float().cpu().numpy() for t in (q, k, v)), 0.125, bias.float().numpy())
+    assert_close(got.float().cpu().numpy(), ref, unit_scale=True)
+
+
+def test_bool_mask_like_sdpa() -> None:
+    gen = torch.Generator().manual_seed(6)
+    q, k, v = (torch.randn(1, 2, 70, 64, generator=gen).half().cuda() for _ in range(3))
+    mask = torch.rand(1, 1, 70, 70, generator=gen) > 0.3
+    mask[..., 0] = True
+    got = ff.scaled_dot_product_attention(q, k, v, attn_mask=mask.cuda())
+    bias = np.where(mask.numpy(), 0.0, -np.inf).astype(np.float32)
+    ref = ao.attention(*(t.float().cpu().numpy() for t in (q, k, v)), 0.125, bias)
+    assert_close(got.float().cpu().numpy(), ref, unit_scale=True)
+
+
+@pytest.mark.parametrize(("hw", "b", "h"), [((14, 14), 25, 12), ((64, 64), 1, 2), ((5, 9), 2, 3)])
+def test_decomposed_bias_sam_shapes(hw: tuple[int, int], b: int, h: int) -> None:
+    """SAM-B's two attention shapes (25 windows of 14x14 tokens; the 64x64 global grid) and a ragged grid."""
+    gen = torch.Generator().manual_seed(hw[0])
+    n = hw[0] * hw[1]
+    q, k, v = (torch.randn(b, h, n, 64, generator=gen).half().cuda() for _ in range(3))
+    rel_h = torch.randn(b, h, n, hw[0], generator=gen).half()
+    rel_w = torch.randn(b, h, n, hw[1], generator=gen).half()
+    got = ff.scaled_dot_product_attention(q, k, v, rel=(rel_h.cuda(), rel_w.cuda()))
+    args = [t.float().cpu().numpy() for t in (q, k, v)]
+    if n > 1024:  # dense bias of the global grid would be 4096^2 per head: check two heads through the C oracle
+        ref = c_oracle.attention(*args, 0.125, rel=(rel_h.float().numpy(), rel_w.float().numpy()), threads=8)
+    else:
+        ref = ao.attention(*args, 0.125, ao.decomposed_bias(rel_h.float().numpy(), rel_w.float().numpy()))
+    assert_close(got.float().cpu().numpy(), ref, unit_scale=True)
+
+
+def test_extreme_range_inputs_give_the_fp32_result() -> None:
+    """The reference's overflow case (tests/test_flash64_guard.py:175-199): q[..., 0] = k[..., 0] = 400 overflows fp16
+    accumulators there and needs its fallback chain; here accumulation is fp32, so the first answer is the fp32 one."""
+    qkv = packed_qkv(1, 300, 2, torch.float16, 1.0, 9)
+    qkv[:, :, 0, :, 0] = 400.0
+    qkv[:, :, 1, :, 0] = 400.0
+    q, k, v = qkv.unbind(2)
+    got = ff.Flash64("hh")(q, k, v, 0.125)
+    assert bool(torch.isfinite(got).all())
+    assert_close(got.float().cpu().numpy(), oracle_of_packed(qkv, 0.125), unit_scale=False)
+
+
+@pytest.mark.parametrize(
+    ("b", "h", "n", "dtype"),
+    [(8, 6, 1370, "fp16"), (4, 16, 1370, "bf16"), (1, 12, 4096, "fp16"), (25, 12, 196, "fp16")],
+)
+def test_full_size_configs_by_properties(b: int, h: int, n: int, dtype: str) -> None:
+    """The benchmark configurations at full size, checked by properties that need no N^2 oracle:
+    v = const -> output = const (rows of P sum to one); permuting the keys leaves the output unchanged;
+    plus an oracle check of a strided sample of heads."""
+    dt = DTYPES[dtype]
+    qkv = packed_qkv(b, n, h, dt, 1.0, n + b)
+    q, k, v = qkv.unbind(2)
+    got = ff.attention(q, k, v, layout="bnhd")
+    ones = torch.full_like(v, 0.5)
+    const = ff.attention(q, k, ones, layout="bnhd")
+    assert float((const.float() - 0.5).abs().max()) <= 4e-3  # one 16-bit rounding of the output
+    perm = torch.randperm(n, generator=torch.Generator().manual_seed(1)).cuda()
+    shuffled = ff.attention(q, k[:, perm], v[:, perm], layout="bnhd")
+    assert float((shuffled.float() - got.float()).abs().max()) <= 2e-2
+    sample = qkv[:: max(1, b // 2), :, :, :: max(1, h // 2)].contiguous()
+    ref = oracle_of_packed(sample, 0.125)
+    assert_close(got[:: max(1, b // 2), :, :: max(1, h // 2)].float().cpu().numpy(), ref, unit_scale=True)
+
+
+def test_two_streams_equal_one_stream() -> None:
+    """Launches on two torch streams give the same bits as on one (the reference checks its kernels the same way,
+    tests/test_threads.py:58-332)."""
+    qkv = packed_qkv(4, 500, 6, torch.float16, 1.0, 21)
+    q, k, v = qkv.unbind(2)
+    base = ff.attention(q, k, v, layout="bnhd")
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    with torch.cuda.stream(s1):
+        a = ff.attention(q, k, v, layout="bnhd")
+    with torch.cuda.stream(s2):
+        b_ = ff.attention(q, k, v, layout="bnhd")
+    torch.cuda.synchronize()
+    assert torch.equal(a, base)
+    assert torch.equal(b_, base)
+
+
+def test_cuda_graph_replay_equals_eager() -> None:
+    """The launch is capturable (families capture whole forwards, src/fastforks/shared/cuda_graphs.py:1-17)."""
+    qkv = packed_qkv(2, 1370, 6, torch.float16, 1.0, 22)
+    q, k, v = qkv.unbind(2)
+    out = torch.empty(2, 1370, 6, 64, dtype=torch.float16, device="cuda")
+    eager = ff.attention(q, k, v, layout="bnhd").clone()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ff.attention(q, k, v, layout="bnhd", out=out)
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
+
+
+def test_contract_violations_raise_before_launch() -> None:
+    q = torch.zeros(1, 5, 2, 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError, match="head dim"):
+        ff.attention(q[..., :32], q[..., :32], q[..., :32], layout="bnhd")
+    with pytest.raises(ValueError, match="unit last stride"):
+        ff.attention(q.transpose(2, 3).contiguous().transpose(2, 3), q, q, layout="bnhd")
+    odd = torch.zeros(1, 5, 2, 68, dtype=torch.float16, device="cuda")[..., 4:]  # token stride 136, base offset 8 bytes
+    with pytest.raises(ValueError, match="aligned|multiple of 8"):
+        ff.attention(odd, odd, odd, layout="bnhd")
+    with pytest.raises(ValueError, match="requires grad"):
+        ff.attention(q.clone().requires_grad_(), q, q, layout="bnhd")
+    with pytest.raises(ValueError, match="exclusive"):
+        ff.attention(q, q, q, layout="bnhd", bias=torch.zeros(5, 5, device="cuda"), rel=(q, q))
