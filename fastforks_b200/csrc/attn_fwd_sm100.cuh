@@ -2,13 +2,16 @@
 //   O = softmax(scale * Q K^T + bias) V,   fp16 / bf16 operands, fp32 accumulation.
 //
 // One CTA owns one or two 128-row query tiles of one (batch, head) and walks the keys in tiles of 128:
-//   * a loader warp stages Q once and K / V tiles through a ring of shared-memory stages with TMA
-//     (128-byte swizzle, rows past the end of the sequence read as zero);
+//   * a loader warp stages Q once and K / V tiles through rings of shared-memory stages with TMA
+//     (128-byte swizzle, rows past the end of the sequence read as zero); K runs two tiles ahead of V;
 //   * an MMA warp issues S = Q K^T (tcgen05.mma, M=128 N=128 K=64) into tensor memory and
-//     O += P V (M=128 N=64 K=128) with P read straight from tensor memory, where it overlays S;
+//     O += P V (M=128 N=64 K=128) with P read straight from tensor memory. S_t(j+2) is issued as soon
+//     as the softmax threads have pulled S_t(j+1) into registers, so the tensor pipe never sits on the
+//     softmax critical path;
 //   * two softmax warpgroups, one per query tile, own one row of S per thread: they read the row
 //     from tensor memory, keep the running maximum and sum, and write P back as 16-bit values.
-//     While one warpgroup runs its exponentials the tensor pipe works for the other tile.
+//     The exponential section is passed between the two warpgroups like a token ("ping-pong"), so
+//     one warpgroup saturates the MUFU unit while the other loads, reduces and stores.
 // The running maximum is only raised when it grows by more than 2^8, so rescaling O (a tensor-memory
 // round trip) is rare; the final division by the row sum happens once in the epilogue.
 //
@@ -26,24 +29,43 @@
 
 namespace b200 {
 
-constexpr int kTileRows = 128;                       // query rows per tile == keys per tile
-constexpr int kHeadDim = 64;                         // the only head dim of this path
-constexpr int kTileBytes = kTileRows * kHeadDim * 2; // one Q / K / V tile in shared memory
-constexpr int kSoftmaxThreads = 256;                 // two warpgroups
+constexpr int kTileRows = 128;                        // query rows per tile == keys per tile
+constexpr int kHeadDim = 64;                          // the only head dim of this path
+constexpr int kTileBytes = kTileRows * kHeadDim * 2;  // one Q / K / V tile in shared memory
 constexpr int kLoaderWarp = 8;
-constexpr int kMmaWarp = 9;
-constexpr int kThreads = 384;                        // 2 softmax warpgroups + 1 warpgroup of helpers (2 idle warps)
-constexpr int kSoftmaxRegs = 224, kHelperRegs = 48;   // per-thread register budgets after the hand-over
+constexpr int kMmaWarp = 9;                             // warps 9 and 10 issue the MMAs of query tile 0 and 1
+constexpr int kThreads = 384;                         // 2 softmax warpgroups + 1 warpgroup of helpers (1 idle warp)
+constexpr int kSoftmaxRegs = 224, kHelperRegs = 56;   // per-thread register budgets after the hand-over
 constexpr int kLaunchRegs = 168;                      // what a 384-thread CTA gets per thread at launch
-// setmaxnreg.inc blocks until the CTA's pool holds the registers: the budgets must fit what the launch allocated,
-// or the second warpgroup waits for ever.
-static_assert(2 * 128 * kSoftmaxRegs + 128 * kHelperRegs <= kLaunchRegs * kThreads, "register hand-over does not balance");
-constexpr uint32_t kTmemCols = 512;                  // S0 S1 (128 each) + O0 O1 (64 each) = 384 -> next power of two
-constexpr uint32_t kTmemS = 0, kTmemO = 256;
+// setmaxnreg.inc blocks until the CTA's pool holds the registers: the budgets must fit what the launch
+// allocated, or the second warpgroup waits for ever.
+static_assert(2 * 128 * kSoftmaxRegs + 128 * kHelperRegs <= kLaunchRegs * kThreads,
+              "register hand-over does not balance");
+constexpr int kStagesK = 4, kStagesV = 4;
+constexpr int kKLead = 2;                             // K tiles are consumed two iterations ahead of V tiles
+constexpr uint32_t kTmemCols = 512;                   // S0 S1 (128 each), O0 O1 (64 each), P0 P1 (64 each)
+constexpr uint32_t kTmemS = 0, kTmemO = 256, kTmemP = 384;
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kRescaleThreshold = 8.0f;            // log2 units: P stays below 2^8 between rescales
+constexpr float kRescaleThreshold = 8.0f;             // log2 units: P stays below 2^8 between rescales
 
 enum : uint32_t { kStatusLoader = 1, kStatusMma = 2, kStatusSoftmax = 4 };
+
+// Development aid, compiled out of the shipped library: with -DB200_TRACE one lane per role of CTA 0 writes
+// clock stamps to AttnParams::trace so that the pipeline's timeline can be read back.
+#ifdef B200_TRACE
+#define B200_STAMP(role, iter, slot)                                                                    \
+  do {                                                                                                  \
+    if (blockIdx.x == 0 && lane == 0 && p.trace != nullptr && (iter) < 32) {                            \
+      long long t_;                                                                                     \
+      asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_));                                                \
+      p.trace[((role) * 32 + (iter)) * 8 + (slot)] = t_;                                                \
+    }                                                                                                   \
+  } while (0)
+#else
+#define B200_STAMP(role, iter, slot) \
+  do {                               \
+  } while (0)
+#endif
 enum : int { kBiasNone = 0, kBiasDense = 1, kBiasDecomposed = 2 };
 
 struct BiasView {
@@ -63,18 +85,22 @@ struct AttnParams {
   BiasView bias2;      // rel_w of the decomposed form
   int rel_kw;
   uint32_t* status;    // device word that collects role bits of expired waits
+  long long* trace;    // development builds only (B200_TRACE), else unused
+  int flags;           // development knobs
 };
 
-template <int STAGES, bool P_IN_SMEM>
 struct alignas(1024) AttnSmem {
   uint8_t q[2][kTileBytes];
-  uint8_t k[STAGES][kTileBytes];
-  uint8_t v[STAGES][kTileBytes];
-  uint8_t p[P_IN_SMEM ? 2 : 1][P_IN_SMEM ? 2 * kTileBytes : 1024];  // P as two 64-key column blocks
+  uint8_t k[kStagesK][kTileBytes];
+  uint8_t v[kStagesV][kTileBytes];
   uint64_t q_full[2];
-  uint64_t k_full[STAGES], k_empty[STAGES];
-  uint64_t v_full[STAGES], v_empty[STAGES];
-  uint64_t s_full[2], p_full[2], o_full[2];
+  uint64_t k_full[kStagesK], k_empty[kStagesK];
+  uint64_t v_full[kStagesV], v_empty[kStagesV];
+  uint64_t s_full[2];   // S_t(j) is in tensor memory                     (MMA commit)
+  uint64_t s_free[2];   // S_t(j) has been read into registers             (4 softmax warps)
+  uint64_t p_full[2];   // P_t(j) is in tensor memory, O_t rescaled        (4 softmax warps)
+  uint64_t pv_done[2];  // O_t += P_t(j) V(j) has finished                 (MMA commit)
+  uint64_t turn[2];     // the other warpgroup is half way through its exponentials: t may start (4 warps)
   uint32_t tmem_base;
   uint32_t abort;
 };
@@ -83,6 +109,63 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// (a.x * b.x + c.x, a.y * b.y + c.y) in one instruction of the FMA pipe.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t"
+      ".reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "mov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t"
+      "}\n"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t"
+      ".reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t"
+      "}\n"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
+// One arrival for the whole warp, after all its lanes have reached this point.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+
+// The same, pinned in the instruction stream: `dep` is routed through the instruction, so every later
+// computation that reads `dep` is scheduled after the arrival instead of being hoisted above it.
+__device__ __forceinline__ void warp_arrive_pinned(uint64_t* bar, int lane, float& dep) {
+  __syncwarp();
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.eq.s32 p, %2, 0;\n\t"
+      "@p mbarrier.arrive.shared::cta.b64 _, [%1];\n\t"
+      "}\n"
+      : "+f"(dep)
+      : "r"(smem_u32(bar)), "r"(lane)
+      : "memory");
 }
 
 template <typename T>
@@ -104,13 +187,12 @@ __device__ __forceinline__ float load_bias_elem(const void* base, int dtype, int
   return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(base) + idx));
 }
 
-template <typename T, int BIAS, int STAGES, bool P_IN_SMEM>
+template <typename T, int BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
-  using Smem = AttnSmem<STAGES, P_IN_SMEM>;
   extern __shared__ uint8_t smem_raw[];
-  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  AttnSmem& sm = *reinterpret_cast<AttnSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -122,20 +204,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int q_row0 = item * 2 * kTileRows;
   const int n_tiles = (p.q_tokens - q_row0 > kTileRows) ? 2 : 1;  // query tiles of this CTA
   const int kv_tiles = p.kv_tiles;
+  // Keys of the last tile, rounded up to the MMA granule: its S needs no more columns, its P V no more steps.
+  const int kv_last = p.kv_tokens - (kv_tiles - 1) * kTileRows;
+  const int kv_last16 = (kv_last + 15) & ~15;
 
   // ---- set-up: barriers, tensor memory -------------------------------------------------------
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sm.q_full[i], 1);
       mbar_init(&sm.s_full[i], 1);
-      mbar_init(&sm.p_full[i], kTileRows);
-      mbar_init(&sm.o_full[i], 1);
+      mbar_init(&sm.s_free[i], 4);  // one arrival per softmax warp: 128 arrivals on one word take hundreds of clocks
+      mbar_init(&sm.p_full[i], 4);
+      mbar_init(&sm.pv_done[i], 1);
+      mbar_init(&sm.turn[i], 4);
     }
-    for (int i = 0; i < STAGES; ++i) {
+    for (int i = 0; i < kStagesK; ++i) {
       mbar_init(&sm.k_full[i], 1);
-      mbar_init(&sm.k_empty[i], 1);
+      mbar_init(&sm.k_empty[i], n_tiles);  // one commit from the MMA thread of every query tile
+    }
+    for (int i = 0; i < kStagesV; ++i) {
       mbar_init(&sm.v_full[i], 1);
-      mbar_init(&sm.v_empty[i], 1);
+      mbar_init(&sm.v_empty[i], n_tiles);
     }
     sm.abort = 0;
     mbar_init_fence();
@@ -157,124 +246,150 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   if (warp >= kLoaderWarp) {
     reg_dealloc<kHelperRegs>();
-  if (warp == kLoaderWarp) {
-    // ======================= loader =========================================================
-    if (lane == 0) {
-      bool ok = true;
-      for (int t = 0; t < n_tiles; ++t) {
-        mbar_arrive_expect_tx(&sm.q_full[t], kTileBytes);
-        tma_load_4d(sm.q[t], &tm_q, &sm.q_full[t], 0, q_row0 + t * kTileRows, h, b);
-      }
-      int issued_k = 0, issued_v = 0;
-      for (int j = 0; j < kv_tiles && ok; ++j) {
-        const int st = j % STAGES;
-        const uint32_t ph = (j / STAGES) & 1;
-        ok = mbar_wait(&sm.k_empty[st], ph ^ 1, abort_flag);
-        if (!ok) break;
-        mbar_arrive_expect_tx(&sm.k_full[st], kTileBytes);
-        tma_load_4d(sm.k[st], &tm_k, &sm.k_full[st], 0, j * kTileRows, h, b);
-        issued_k = j + 1;
-        ok = mbar_wait(&sm.v_empty[st], ph ^ 1, abort_flag);
-        if (!ok) break;
-        mbar_arrive_expect_tx(&sm.v_full[st], kTileBytes);
-        tma_load_4d(sm.v[st], &tm_v, &sm.v_full[st], 0, j * kTileRows, h, b);
-        issued_v = j + 1;
-      }
-      if (!ok) {
-        if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusLoader);
-      }
-      if (*abort_flag != 0) {
-        // Nobody may be consuming any more: wait (bounded, ignoring the abort flag) for every copy
-        // that was issued, so that none writes into shared memory after the CTA has gone.
-        uint32_t no_abort = 0;
-        for (int t = 0; t < n_tiles; ++t) mbar_wait(&sm.q_full[t], 0, &no_abort);
-        for (int j = (issued_k > STAGES ? issued_k - STAGES : 0); j < issued_k; ++j)
-          mbar_wait(&sm.k_full[j % STAGES], (j / STAGES) & 1, &no_abort);
-        for (int j = (issued_v > STAGES ? issued_v - STAGES : 0); j < issued_v; ++j)
-          mbar_wait(&sm.v_full[j % STAGES], (j / STAGES) & 1, &no_abort);
-      }
-    }
-    __syncwarp();
-  } else if (warp == kMmaWarp) {
-    // ======================= MMA issuer ======================================================
-    if (lane == 0) {
-      constexpr uint32_t fmt = std::is_same<T, __half>::value ? UMMA_F16 : UMMA_BF16;
-      constexpr uint32_t idesc_qk = umma_idesc_f16(fmt, kTileRows, kTileRows, 0, 0);
-      constexpr uint32_t idesc_pv = umma_idesc_f16(fmt, kTileRows, kHeadDim, 0, 1);
-      bool ok = true;
-
-      auto issue_qk = [&](int t, int st) {
-        const uint64_t a = umma_smem_desc_sw128(smem_u32(sm.q[t]), 1024, 16);
-        const uint64_t bd = umma_smem_desc_sw128(smem_u32(sm.k[st]), 1024, 16);
-#pragma unroll
-        for (int kk = 0; kk < kHeadDim / 16; ++kk)  // 32 bytes of K per step inside the swizzle atom
-          umma_ss(tmem + kTmemS + t * kTileRows, a + 2 * kk, bd + 2 * kk, idesc_qk, kk > 0);
-      };
-      auto issue_pv = [&](int t, int st, bool first) {
-        const uint64_t bd = umma_smem_desc_sw128(smem_u32(sm.v[st]), 1024, 0);
-#pragma unroll
-        for (int kk = 0; kk < kTileRows / 16; ++kk) {  // 16 keys = two 8-row groups of V per step
-          const uint32_t acc = (!first || kk > 0) ? 1u : 0u;
-          if constexpr (P_IN_SMEM) {
-            const uint64_t a =
-                umma_smem_desc_sw128(smem_u32(sm.p[t]) + (kk / 4) * kTileBytes, 1024, 16) + 2 * (kk % 4);
-            umma_ss(tmem + kTmemO + t * kHeadDim, a, bd + kk * (2048 >> 4), idesc_pv, acc);
-          } else {
-            umma_ts(tmem + kTmemO + t * kHeadDim, tmem + kTmemS + t * kTileRows + kk * 8, bd + kk * (2048 >> 4),
-                    idesc_pv, acc);
+    if (warp == kLoaderWarp) {
+      // ======================= loader =======================================================
+      if (lane == 0) {
+        bool ok = true;
+        for (int t = 0; t < n_tiles; ++t) {
+          mbar_arrive_expect_tx(&sm.q_full[t], kTileBytes);
+          tma_load_4d(sm.q[t], &tm_q, &sm.q_full[t], 0, q_row0 + t * kTileRows, h, b);
+        }
+        int issued_k = 0, issued_v = 0;
+        for (int i = 0; i < kv_tiles + kKLead && ok; ++i) {
+          if (i < kv_tiles) {
+            const int st = i % kStagesK;
+            ok = mbar_wait(&sm.k_empty[st], ((i / kStagesK) & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            mbar_arrive_expect_tx(&sm.k_full[st], kTileBytes);
+            tma_load_4d(sm.k[st], &tm_k, &sm.k_full[st], 0, i * kTileRows, h, b);
+            issued_k = i + 1;
+          }
+          const int jv = i - kKLead;
+          if (jv >= 0) {
+            const int st = jv % kStagesV;
+            ok = mbar_wait(&sm.v_empty[st], ((jv / kStagesV) & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            mbar_arrive_expect_tx(&sm.v_full[st], kTileBytes);
+            tma_load_4d(sm.v[st], &tm_v, &sm.v_full[st], 0, jv * kTileRows, h, b);
+            issued_v = jv + 1;
           }
         }
-      };
-
-      // S_t(0) for both tiles
-      ok = mbar_wait(&sm.k_full[0], 0, abort_flag);
-      for (int t = 0; t < n_tiles && ok; ++t) {
-        ok = mbar_wait(&sm.q_full[t], 0, abort_flag);
-        if (!ok) break;
-        tc_fence_after_sync();
-        issue_qk(t, 0);
-        umma_commit(&sm.s_full[t]);
-      }
-      if (ok) umma_commit(&sm.k_empty[0]);
-
-      for (int j = 0; j < kv_tiles && ok; ++j) {
-        const int st = j % STAGES;
-        const uint32_t ph = (j / STAGES) & 1;
-        const bool more = j + 1 < kv_tiles;
-        const int st1 = (j + 1) % STAGES;
-        const uint32_t ph1 = ((j + 1) / STAGES) & 1;
-        if (more) {
-          ok = mbar_wait(&sm.k_full[st1], ph1, abort_flag);
-          if (!ok) break;
+        if (!ok) {
+          if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusLoader);
         }
-        ok = mbar_wait(&sm.v_full[st], ph, abort_flag);
-        if (!ok) break;
-        for (int t = 0; t < n_tiles; ++t) {
-          ok = mbar_wait(&sm.p_full[t], j & 1, abort_flag);
+        if (*abort_flag != 0) {
+          // Nobody may be consuming any more: wait (bounded, ignoring the abort flag) for every copy
+          // that was issued, so that none writes into shared memory after the CTA has gone.
+          uint32_t no_abort = 0;
+          for (int t = 0; t < n_tiles; ++t) mbar_wait(&sm.q_full[t], 0, &no_abort);
+          for (int j = (issued_k > kStagesK ? issued_k - kStagesK : 0); j < issued_k; ++j)
+            mbar_wait(&sm.k_full[j % kStagesK], (j / kStagesK) & 1, &no_abort);
+          for (int j = (issued_v > kStagesV ? issued_v - kStagesV : 0); j < issued_v; ++j)
+            mbar_wait(&sm.v_full[j % kStagesV], (j / kStagesV) & 1, &no_abort);
+        }
+      }
+      __syncwarp();
+    } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
+      // ======================= MMA issuers: one thread per query tile ==========================
+      const int t = warp - kMmaWarp;
+      if (lane == 0 && t < n_tiles) {
+        constexpr uint32_t fmt = std::is_same<T, __half>::value ? UMMA_F16 : UMMA_BF16;
+        constexpr uint32_t idesc_qk = umma_idesc_f16(fmt, kTileRows, kTileRows, 0, 0);
+        constexpr uint32_t idesc_pv = umma_idesc_f16(fmt, kTileRows, kHeadDim, 0, 1);
+        const uint32_t idesc_qk_last = umma_idesc_f16(fmt, kTileRows, kv_last16, 0, 0);
+        bool ok = true;
+
+        // Everything the issue loops need is computed once: one thread feeds the tensor pipe, and every
+        // instruction between two tcgen05.mma shows up as an idle pipe when the MMAs are this small.
+        const uint64_t q_desc = umma_smem_desc_sw128(smem_u32(sm.q[t]), 1024, 16);
+        const uint64_t k_desc0 = umma_smem_desc_sw128(smem_u32(sm.k[0]), 1024, 16);
+        const uint64_t v_desc0 = umma_smem_desc_sw128(smem_u32(sm.v[0]), 1024, 0);
+        constexpr uint64_t kStageStep = kTileBytes >> 4;  // descriptor distance between two ring stages
+        const uint32_t s_tm = tmem + kTmemS + t * kTileRows;
+        const uint32_t o_tm = tmem + kTmemO + t * kHeadDim;
+        const uint32_t p_tm = tmem + kTmemP + t * kHeadDim;
+        uint64_t* const s_full = &sm.s_full[t];
+        uint64_t* const s_free = &sm.s_free[t];
+        uint64_t* const p_full = &sm.p_full[t];
+        uint64_t* const pv_done = &sm.pv_done[t];
+
+        // S_t(j) = Q_t K_j^T. The last key tile only computes the columns that hold keys.
+        auto issue_qk = [&](int j) {
+          const int st = j % kStagesK;
+          const uint64_t bd = k_desc0 + static_cast<uint64_t>(st) * kStageStep;
+          const uint32_t idesc = (j == kv_tiles - 1) ? idesc_qk_last : idesc_qk;
+#pragma unroll
+          for (int kk = 0; kk < kHeadDim / 16; ++kk)  // 32 bytes of K per step inside the swizzle atom
+            umma_ss(s_tm, q_desc + 2 * kk, bd + 2 * kk, idesc, kk > 0 ? 1u : 0u);
+          umma_commit(s_full);
+          umma_commit(&sm.k_empty[st]);
+        };
+        // O_t (+)= P_t(j) V_j, 16 keys (two 8-row groups of the V tile) per step.
+        auto issue_pv = [&](int j) {
+          const int st = j % kStagesV;
+          const uint64_t bd = v_desc0 + static_cast<uint64_t>(st) * kStageStep;
+          if (j != kv_tiles - 1) {
+            umma_ts(o_tm, p_tm, bd, idesc_pv, j > 0 ? 1u : 0u);
+#pragma unroll
+            for (int kk = 1; kk < kTileRows / 16; ++kk)
+              umma_ts(o_tm, p_tm + kk * 8, bd + kk * (2048 >> 4), idesc_pv, 1u);
+          } else {
+            const int steps = kv_last16 / 16;  // at least one
+            umma_ts(o_tm, p_tm, bd, idesc_pv, j > 0 ? 1u : 0u);
+#pragma unroll
+            for (int kk = 1; kk < kTileRows / 16; ++kk)
+              if (kk < steps) umma_ts(o_tm, p_tm + kk * 8, bd + kk * (2048 >> 4), idesc_pv, 1u);
+          }
+          B200_STAMP(2 + t, j, 4);
+          umma_commit(pv_done);
+          umma_commit(&sm.v_empty[st]);
+        };
+        auto k_ready = [&](int j) { return mbar_wait(&sm.k_full[j % kStagesK], (j / kStagesK) & 1, abort_flag); };
+        auto v_ready = [&](int j) { return mbar_wait(&sm.v_full[j % kStagesV], (j / kStagesV) & 1, abort_flag); };
+
+        // S_t(0), then S_t(1) as soon as S_t(0) sits in registers.
+        ok = k_ready(0) && mbar_wait(&sm.q_full[t], 0, abort_flag);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_qk(0);
+        }
+        if (ok && kv_tiles > 1) {
+          ok = k_ready(1) && mbar_wait(s_free, 0, abort_flag);
+          if (ok) {
+            tc_fence_after_sync();
+            issue_qk(1);
+          }
+        }
+        // Steady state: P_t(j) -> PV_t(j);  S_t(j+1) read -> QK_t(j+2).
+        for (int j = 0; j < kv_tiles && ok; ++j) {
+          const bool ahead = j + 2 < kv_tiles;
+          ok = v_ready(j) && mbar_wait(p_full, j & 1, abort_flag);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_pv(t, st, j == 0);
-          if (more) {
-            issue_qk(t, st1);
-            umma_commit(&sm.s_full[t]);
-          } else {
-            umma_commit(&sm.o_full[t]);
+          B200_STAMP(2 + t, j, 0);
+          issue_pv(j);
+          B200_STAMP(2 + t, j, 1);
+          if (ahead) {
+            ok = k_ready(j + 2);
+            B200_STAMP(2 + t, j, 5);
+            ok = ok && mbar_wait(s_free, (j + 1) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after_sync();
+            B200_STAMP(2 + t, j, 2);
+            issue_qk(j + 2);
+            B200_STAMP(2 + t, j, 3);
           }
         }
-        if (!ok) break;
-        umma_commit(&sm.v_empty[st]);
-        if (more) umma_commit(&sm.k_empty[st1]);
+        if (!ok) {
+          if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusMma);
+        }
       }
-      if (!ok) {
-        if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusMma);
-      }
+      __syncwarp();
     }
-    __syncwarp();
-  }
   } else {
-    // ======================= softmax warpgroups ==============================================
+    // ======================= softmax warpgroups ================================================
     reg_alloc<kSoftmaxRegs>();
-    const int t = warp >> 2;                     // query tile of this warpgroup
+    const int t = warp >> 2;  // query tile of this warpgroup
     const int row_in_tile = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     if (t < n_tiles) {
@@ -282,7 +397,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const bool row_valid = q_row < p.q_tokens;
       const uint32_t s_addr = tmem + lane_addr + kTmemS + t * kTileRows;
       const uint32_t o_addr = tmem + lane_addr + kTmemO + t * kHeadDim;
+      const uint32_t p_addr = tmem + lane_addr + kTmemP + t * kHeadDim;
       const float c = p.scale_log2;
+      const bool pingpong = n_tiles == 2 && !(p.flags & 1);
       float m_ref = -INFINITY;
       float l_sum = 0.f;
       bool ok = true;
@@ -298,6 +415,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_full[t], j & 1, abort_flag));
         if (!ok) break;
         tc_fence_after_sync();
+        if ((warp & 3) == 0) B200_STAMP(t, j, 0);
 
         float s[kTileRows];
         {
@@ -305,6 +423,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_ld_x64(s_addr, su);
           tmem_ld_x64(s_addr + 64, su + 64);
         }
+        // S_t is in registers: the tensor pipe may overwrite it with the tile after next.
+        tc_fence_before_sync();
+        warp_arrive(&sm.s_free[t], lane);
+        if ((warp & 3) == 0) B200_STAMP(t, j, 1);
+
         const int kv0 = j * kTileRows;
         const int kv_valid = min(kTileRows, p.kv_tokens - kv0);
 
@@ -317,7 +440,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         } else if constexpr (BIAS == kBiasDecomposed) {
           int ih = kv0 / p.rel_kw;
           int iw = kv0 - ih * p.rel_kw;
-          float bh_val = (kv0 < p.kv_tokens) ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih) : 0.f;
+          float bh_val = load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih);
 #pragma unroll
           for (int i = 0; i < kTileRows; ++i) {
             float bv = 0.f;
@@ -336,14 +459,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (i >= kv_valid) s[i] = -INFINITY;
         }
 
-        float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+        float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
+        float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
 #pragma unroll
-        for (int i = 4; i < kTileRows; i += 4) {
-          mx0 = fmaxf(mx0, s[i]);
-          mx1 = fmaxf(mx1, s[i + 1]);
-          mx2 = fmaxf(mx2, s[i + 2]);
-          mx3 = fmaxf(mx3, s[i + 3]);
+        for (int i = 12; i + 7 < kTileRows; i += 8) {
+          mx0 = max3(mx0, s[i], s[i + 1]);
+          mx1 = max3(mx1, s[i + 2], s[i + 3]);
+          mx2 = max3(mx2, s[i + 4], s[i + 5]);
+          mx3 = max3(mx3, s[i + 6], s[i + 7]);
         }
+        mx0 = max3(mx0, s[124], s[125]);  // 12 + 8 * 14 = 124: four columns left
+        mx1 = max3(mx1, s[126], s[127]);
         float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         if constexpr (BIAS == kBiasNone) m_tile *= c;
 
@@ -354,64 +480,73 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           alpha = fast_exp2(m_ref - m_tile);  // m_ref = -inf -> 0
           m_ref = m_tile;
         }
-        if (j > 0 && __any_sync(0xffffffffu, raise)) {
-          float o[kHeadDim];
-          uint32_t* ou = reinterpret_cast<uint32_t*>(o);
-          tmem_ld_x64(o_addr, ou);
-#pragma unroll
-          for (int i = 0; i < kHeadDim; ++i) o[i] *= alpha;
-          tmem_st_x32(o_addr, ou);
-          tmem_st_x32(o_addr + 32, ou + 32);
-        }
         l_sum *= alpha;
         const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
 
-        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+        if ((warp & 3) == 0) B200_STAMP(t, j, 6);
+
+        // ---- exponentials ---------------------------------------------------------------------------
+        // Both warpgroups feed the MUFU unit, but they must not run in lockstep (their loads and reductions
+        // would leave the unit idle together, and equal loops sharing a unit drift into lockstep). So each
+        // may only start a section once the other is half way through its previous one: warpgroup 0 starts
+        // tile j+1 after warpgroup 1's midpoint of tile j, warpgroup 1 starts tile j after warpgroup 0's
+        // midpoint of tile j. Half a section apart, neither ever waits here.
+        if (pingpong && (t == 1 || j > 0)) {
+          const uint32_t parity = (t == 0) ? ((j - 1) & 1) : (j & 1);
+          ok = __all_sync(0xffffffffu, mbar_wait(&sm.turn[t], parity, abort_flag));
+          if (!ok) break;
+        }
+        if ((warp & 3) == 0) B200_STAMP(t, j, 2);
+        float2 l2a = make_float2(0.f, 0.f), l2b = make_float2(0.f, 0.f);
+        const float2 c2 = (BIAS == kBiasNone) ? make_float2(c, c) : make_float2(1.f, 1.f);
+        float nm = -m_use;
         uint32_t pk[kTileRows / 2];
 #pragma unroll
-        for (int i = 0; i < kTileRows; i += 4) {
-          float p0, p1, p2, p3;
-          if constexpr (BIAS == kBiasNone) {
-            p0 = fast_exp2(fmaf(s[i], c, -m_use));
-            p1 = fast_exp2(fmaf(s[i + 1], c, -m_use));
-            p2 = fast_exp2(fmaf(s[i + 2], c, -m_use));
-            p3 = fast_exp2(fmaf(s[i + 3], c, -m_use));
-          } else {
-            p0 = fast_exp2(s[i] - m_use);
-            p1 = fast_exp2(s[i + 1] - m_use);
-            p2 = fast_exp2(s[i + 2] - m_use);
-            p3 = fast_exp2(s[i + 3] - m_use);
-          }
-          l0 += p0;
-          l1 += p1;
-          l2 += p2;
-          l3 += p3;
-          pk[i / 2] = pack2<T>(p0, p1);
-          pk[i / 2 + 1] = pack2<T>(p2, p3);
-        }
-        l_sum += (l0 + l1) + (l2 + l3);
-
-        if constexpr (P_IN_SMEM) {
-          // Row r of the K-major, 128-byte-swizzled P tile: 16-byte chunk c of a 64-key block sits at
-          // r * 128 + ((c ^ (r & 7)) * 16).
-          uint8_t* prow = sm.p[t] + row_in_tile * 128;
+        for (int half = 0; half < 2; ++half) {
+          const float2 nm2 = make_float2(nm, nm);
 #pragma unroll
-          for (int ch = 0; ch < 16; ++ch) {
-            uint4 val = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-            uint8_t* dst = prow + (ch / 8) * kTileBytes + (((ch & 7) ^ (row_in_tile & 7)) << 4);
-            *reinterpret_cast<uint4*>(dst) = val;
+          for (int i = half * (kTileRows / 2); i < (half + 1) * (kTileRows / 2); i += 4) {
+            const float2 xa = ffma2(make_float2(s[i], s[i + 1]), c2, nm2);
+            const float2 xb = ffma2(make_float2(s[i + 2], s[i + 3]), c2, nm2);
+            const float2 pa = make_float2(fast_exp2(xa.x), fast_exp2(xa.y));
+            const float2 pb = make_float2(fast_exp2(xb.x), fast_exp2(xb.y));
+            l2a = fadd2(l2a, pa);
+            l2b = fadd2(l2b, pb);
+            pk[i / 2] = pack2<T>(pa.x, pa.y);
+            pk[i / 2 + 1] = pack2<T>(pb.x, pb.y);
           }
-          fence_proxy_async_smem();
-        } else {
-          tmem_st_x32(s_addr, pk);
-          tmem_st_x32(s_addr + 32, pk + 32);
+          // Midpoint: let the other warpgroup start. The second half reads `nm` through the arrival.
+          if (half == 0 && pingpong) warp_arrive_pinned(&sm.turn[t ^ 1], lane, nm);
         }
+        if ((warp & 3) == 0) B200_STAMP(t, j, 3);
+        l_sum += (l2a.x + l2a.y) + (l2b.x + l2b.y);
+
+        // P_t and O_t may only change once P_t(j-1) V has finished: it was issued when this warpgroup
+        // delivered P_t(j-1), a whole exponential section ago.
+        if (j > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done[t], (j - 1) & 1, abort_flag));
+          if (!ok) break;
+          tc_fence_after_sync();
+          if (__any_sync(0xffffffffu, raise)) {
+            float o[kHeadDim];
+            uint32_t* ou = reinterpret_cast<uint32_t*>(o);
+            tmem_ld_x64(o_addr, ou);
+#pragma unroll
+            for (int i = 0; i < kHeadDim; ++i) o[i] *= alpha;
+            tmem_st_x32(o_addr, ou);
+            tmem_st_x32(o_addr + 32, ou + 32);
+          }
+        }
+        if ((warp & 3) == 0) B200_STAMP(t, j, 4);
+        tmem_st_x32(p_addr, pk);
+        tmem_st_x32(p_addr + 32, pk + 32);
         tmem_st_wait();
         tc_fence_before_sync();
-        mbar_arrive(&sm.p_full[t]);
+        warp_arrive(&sm.p_full[t], lane);
+        if ((warp & 3) == 0) B200_STAMP(t, j, 5);
       }
 
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.o_full[t], 0, abort_flag));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done[t], (kv_tiles - 1) & 1, abort_flag));
       if (ok) {
         tc_fence_after_sync();
         float o[kHeadDim];

@@ -8,6 +8,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -21,6 +22,10 @@ using namespace b200;
 __device__ uint32_t g_status_word;
 
 thread_local char tl_error[512] = "";
+
+#ifdef B200_TRACE
+long long* g_trace_buffer = nullptr;  // development builds only
+#endif
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -155,13 +160,11 @@ int validate(const B200AttnArgs* a, int* bias_mode, int* schedule) {
   return B200_ATTN_OK;
 }
 
-constexpr int kStages = 4;
-
 template <typename T, int BIAS>
 int launch(const B200AttnArgs* a, const AttnParams& prm, const CUtensorMap& mq, const CUtensorMap& mk,
            const CUtensorMap& mv, cudaStream_t stream) {
-  auto kernel = attn_fwd_kernel<T, BIAS, kStages, false>;
-  constexpr int smem = static_cast<int>(sizeof(AttnSmem<kStages, false>)) + 1024;
+  auto kernel = attn_fwd_kernel<T, BIAS>;
+  constexpr int smem = static_cast<int>(sizeof(AttnSmem)) + 1024;
   // The opt-in is per device and per kernel; setting it again is cheap and keeps this path stateless.
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(shared memory)");
@@ -220,6 +223,10 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
   cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&prm.status), g_status_word);
   if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(status word)");
 
+#ifdef B200_TRACE
+  prm.trace = g_trace_buffer;
+#endif
+  if (const char* f = std::getenv("B200_ATTN_FLAGS")) prm.flags = std::atoi(f);
   const bool f16 = a->dtype == B200_ATTN_F16;
   switch (bias_mode) {
     case kBiasNone:
@@ -248,6 +255,10 @@ int b200_attn_status(uint32_t* status) {
   *status = word;
   return B200_ATTN_OK;
 }
+
+#ifdef B200_TRACE
+void b200_attn_debug_set_trace(void* device_buffer) { g_trace_buffer = static_cast<long long*>(device_buffer); }
+#endif
 
 const char* b200_attn_last_error(void) { return tl_error; }
 

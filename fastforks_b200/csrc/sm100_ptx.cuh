@@ -54,6 +54,17 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t done;
+#ifdef B200_TEST_WAIT
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+#else
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
@@ -63,6 +74,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(done)
       : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
+#endif
   return done != 0;
 }
 
@@ -73,13 +85,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Waits for the phase with the given parity to complete. Returns false when the limit ran out or
 // when another thread of the CTA has already raised `*abort_flag` (shared memory).
+// The wall clock is only consulted after a long run of failed polls (each try_wait already sleeps in
+// hardware for a while), so a wait that succeeds quickly costs a handful of instructions.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+  for (uint32_t polls = 0; polls < 4096; ++polls)
+    if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t polls = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++polls & 0x3ff) == 0) {
+    if ((++polls & 0xff) == 0) {
       if (*abort_flag != 0) return false;
       if (global_timer_ns() - t0 > B200_WAIT_LIMIT_NS) return false;
     }
