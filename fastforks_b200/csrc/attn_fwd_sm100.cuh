@@ -1,7 +1,8 @@
 // Non-causal multi-head attention forward for head dim 64 on sm_100a:
 //   O = softmax(scale * Q K^T + bias) V,   fp16 / bf16 operands, fp32 accumulation.
 //
-// One CTA owns one or two 128-row query tiles of one (batch, head) and walks the keys in tiles of 128:
+// Persistent CTAs (one per SM) take work items - one or two 128-row query tiles of one (batch, head) - and walk
+// the keys of each in tiles of 128:
 //   * a loader warp stages Q once and K / V tiles through rings of shared-memory stages with TMA
 //     (128-byte swizzle, rows past the end of the sequence read as zero); K runs two tiles ahead of V;
 //   * an MMA warp issues S = Q K^T (tcgen05.mma, M=128 N=128 K=64) into tensor memory and
@@ -76,7 +77,8 @@ struct BiasView {
 
 struct AttnParams {
   int batch, heads, q_tokens, kv_tokens;
-  int items_per_head;  // CTAs per (batch, head): ceil(q_tiles / 2)
+  int items_per_head;  // work items per (batch, head): ceil(q_tiles / 2)
+  int q_tiles;         // 128-row query tiles per (batch, head)
   int kv_tiles;
   float scale_log2;    // scale * log2(e)
   void* o;
@@ -93,13 +95,15 @@ struct alignas(1024) AttnSmem {
   uint8_t q[2][kTileBytes];
   uint8_t k[kStagesK][kTileBytes];
   uint8_t v[kStagesV][kTileBytes];
-  uint64_t q_full[2];
+  uint64_t q_full[2];   // Q_t of the current item has landed                (TMA)
+  uint64_t q_empty[2];  // the item's last Q_t K^T has finished               (MMA commit)
   uint64_t k_full[kStagesK], k_empty[kStagesK];
   uint64_t v_full[kStagesV], v_empty[kStagesV];
   uint64_t s_full[2];   // S_t(j) is in tensor memory                     (MMA commit)
   uint64_t s_free[2];   // S_t(j) has been read into registers             (4 softmax warps)
   uint64_t p_full[2];   // P_t(j) is in tensor memory, O_t rescaled        (4 softmax warps)
   uint64_t pv_done[2];  // O_t += P_t(j) V(j) has finished                 (MMA commit)
+  uint64_t o_free[2];   // the item's O_t has been read by its epilogue     (4 softmax warps)
   uint64_t turn[2];     // the other warpgroup is half way through its exponentials: t may start (4 warps)
   uint32_t tmem_base;
   uint32_t abort;
@@ -147,6 +151,17 @@ __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
   return d;
 }
 
+// Spins for `clocks` SM cycles. A tcgen05.mma that finds the tensor pipe's queue full stalls at dispatch and
+// takes the issue port of its SM sub-partition with it, which starves the softmax warps that live there; an issuer
+// that waits out the previous MMA before sending the next one never hits a full queue.
+__device__ __forceinline__ void pace(long long& last, int clocks) {
+  long long now;
+  do {
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(now));
+  } while (now - last < clocks);
+  last = now;
+}
+
 // One arrival for the whole warp, after all its lanes have reached this point.
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   __syncwarp();
@@ -187,6 +202,37 @@ __device__ __forceinline__ float load_bias_elem(const void* base, int dtype, int
   return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(base) + idx));
 }
 
+// One unit of work: one or two 128-row query tiles of one (batch, head).
+struct WorkItem {
+  int b, h, q_row0, n_tiles;
+};
+
+// Items are numbered with all two-tile items first and the one-tile items (the odd last tile of each head) after
+// them. A CTA takes every gridDim.x-th item, so its own list also runs from two-tile to one-tile items: the second
+// warpgroup and its MMA thread finish their last item and leave, they never have to skip one in the middle (a role
+// that skips barrier phases cannot wait on them by parity any more). Long items first also balances the tail.
+__device__ __forceinline__ WorkItem decode_item(const AttnParams& p, int item_id) {
+  WorkItem w;
+  const int pairs = p.q_tiles >> 1;  // two-tile items per head
+  const int doubles = pairs * p.batch * p.heads;
+  int bh;
+  if (item_id < doubles) {
+    bh = item_id / pairs;
+    w.q_row0 = (item_id - bh * pairs) * 2 * kTileRows;
+    w.n_tiles = 2;
+  } else {
+    bh = item_id - doubles;
+    w.q_row0 = pairs * 2 * kTileRows;
+    w.n_tiles = 1;
+  }
+  w.b = bh / p.heads;
+  w.h = bh % p.heads;
+  return w;
+}
+
+// Persistent kernel: CTA c works on items c, c + gridDim.x, c + 2 gridDim.x, ... All barrier phases and ring
+// positions are running counters, so the loader prefetches the next item's Q / K / V while the current one is
+// still being computed and tensor memory and barriers are set up once per CTA.
 template <typename T, int BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -197,12 +243,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int item = blockIdx.x % p.items_per_head;
-  const int bh = blockIdx.x / p.items_per_head;
-  const int b = bh / p.heads;
-  const int h = bh % p.heads;
-  const int q_row0 = item * 2 * kTileRows;
-  const int n_tiles = (p.q_tokens - q_row0 > kTileRows) ? 2 : 1;  // query tiles of this CTA
+  const int total_items = p.items_per_head * p.batch * p.heads;
+  const int my_items = (total_items - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                       static_cast<int>(gridDim.x);
   const int kv_tiles = p.kv_tiles;
   // Keys of the last tile, rounded up to the MMA granule: its S needs no more columns, its P V no more steps.
   const int kv_last = p.kv_tokens - (kv_tiles - 1) * kTileRows;
@@ -212,19 +255,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sm.q_full[i], 1);
+      mbar_init(&sm.q_empty[i], 1);
       mbar_init(&sm.s_full[i], 1);
       mbar_init(&sm.s_free[i], 4);  // one arrival per softmax warp: 128 arrivals on one word take hundreds of clocks
       mbar_init(&sm.p_full[i], 4);
       mbar_init(&sm.pv_done[i], 1);
+      mbar_init(&sm.o_free[i], 4);
       mbar_init(&sm.turn[i], 4);
     }
     for (int i = 0; i < kStagesK; ++i) {
       mbar_init(&sm.k_full[i], 1);
-      mbar_init(&sm.k_empty[i], n_tiles);  // one commit from the MMA thread of every query tile
+      mbar_init(&sm.k_empty[i], 2);  // one commit per query tile (an item with one tile commits twice)
     }
     for (int i = 0; i < kStagesV; ++i) {
       mbar_init(&sm.v_full[i], 1);
-      mbar_init(&sm.v_empty[i], n_tiles);
+      mbar_init(&sm.v_empty[i], 2);
     }
     sm.abort = 0;
     mbar_init_fence();
@@ -250,28 +295,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // ======================= loader =======================================================
       if (lane == 0) {
         bool ok = true;
-        for (int t = 0; t < n_tiles; ++t) {
-          mbar_arrive_expect_tx(&sm.q_full[t], kTileBytes);
-          tma_load_4d(sm.q[t], &tm_q, &sm.q_full[t], 0, q_row0 + t * kTileRows, h, b);
-        }
-        int issued_k = 0, issued_v = 0;
-        for (int i = 0; i < kv_tiles + kKLead && ok; ++i) {
-          if (i < kv_tiles) {
-            const int st = i % kStagesK;
-            ok = mbar_wait(&sm.k_empty[st], ((i / kStagesK) & 1) ^ 1, abort_flag);
+        int gk = 0, gv = 0;        // K / V tiles issued so far (ring position and phase)
+        int q_count[2] = {0, 0};   // Q tiles issued so far per query-tile slot
+        for (int it = 0; it < my_items && ok; ++it) {
+          const WorkItem w = decode_item(p, blockIdx.x + it * gridDim.x);
+          for (int t = 0; t < w.n_tiles && ok; ++t) {
+            if (q_count[t] > 0) ok = mbar_wait(&sm.q_empty[t], (q_count[t] - 1) & 1, abort_flag);
             if (!ok) break;
-            mbar_arrive_expect_tx(&sm.k_full[st], kTileBytes);
-            tma_load_4d(sm.k[st], &tm_k, &sm.k_full[st], 0, i * kTileRows, h, b);
-            issued_k = i + 1;
+            mbar_arrive_expect_tx(&sm.q_full[t], kTileBytes);
+            tma_load_4d(sm.q[t], &tm_q, &sm.q_full[t], 0, w.q_row0 + t * kTileRows, w.h, w.b);
+            ++q_count[t];
           }
-          const int jv = i - kKLead;
-          if (jv >= 0) {
-            const int st = jv % kStagesV;
-            ok = mbar_wait(&sm.v_empty[st], ((jv / kStagesV) & 1) ^ 1, abort_flag);
-            if (!ok) break;
-            mbar_arrive_expect_tx(&sm.v_full[st], kTileBytes);
-            tma_load_4d(sm.v[st], &tm_v, &sm.v_full[st], 0, jv * kTileRows, h, b);
-            issued_v = jv + 1;
+          for (int i = 0; i < kv_tiles + kKLead && ok; ++i) {
+            if (i < kv_tiles) {
+              const int st = gk % kStagesK;
+              ok = mbar_wait(&sm.k_empty[st], ((gk / kStagesK) & 1) ^ 1, abort_flag);
+              if (!ok) break;
+              mbar_arrive_expect_tx(&sm.k_full[st], kTileBytes);
+              tma_load_4d(sm.k[st], &tm_k, &sm.k_full[st], 0, i * kTileRows, w.h, w.b);
+              ++gk;
+            }
+            const int jv = i - kKLead;
+            if (jv >= 0) {
+              const int st = gv % kStagesV;
+              ok = mbar_wait(&sm.v_empty[st], ((gv / kStagesV) & 1) ^ 1, abort_flag);
+              if (!ok) break;
+              mbar_arrive_expect_tx(&sm.v_full[st], kTileBytes);
+              tma_load_4d(sm.v[st], &tm_v, &sm.v_full[st], 0, jv * kTileRows, w.h, w.b);
+              ++gv;
+            }
           }
         }
         if (!ok) {
@@ -281,10 +333,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // Nobody may be consuming any more: wait (bounded, ignoring the abort flag) for every copy
           // that was issued, so that none writes into shared memory after the CTA has gone.
           uint32_t no_abort = 0;
-          for (int t = 0; t < n_tiles; ++t) mbar_wait(&sm.q_full[t], 0, &no_abort);
-          for (int j = (issued_k > kStagesK ? issued_k - kStagesK : 0); j < issued_k; ++j)
+          for (int t = 0; t < 2; ++t)
+            if (q_count[t] > 0) mbar_wait(&sm.q_full[t], (q_count[t] - 1) & 1, &no_abort);
+          for (int j = (gk > kStagesK ? gk - kStagesK : 0); j < gk; ++j)
             mbar_wait(&sm.k_full[j % kStagesK], (j / kStagesK) & 1, &no_abort);
-          for (int j = (issued_v > kStagesV ? issued_v - kStagesV : 0); j < issued_v; ++j)
+          for (int j = (gv > kStagesV ? gv - kStagesV : 0); j < gv; ++j)
             mbar_wait(&sm.v_full[j % kStagesV], (j / kStagesV) & 1, &no_abort);
         }
       }
@@ -292,7 +345,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
       // ======================= MMA issuers: one thread per query tile ==========================
       const int t = warp - kMmaWarp;
-      if (lane == 0 && t < n_tiles) {
+      if (lane == 0) {
         constexpr uint32_t fmt = std::is_same<T, __half>::value ? UMMA_F16 : UMMA_BF16;
         constexpr uint32_t idesc_qk = umma_idesc_f16(fmt, kTileRows, kTileRows, 0, 0);
         constexpr uint32_t idesc_pv = umma_idesc_f16(fmt, kTileRows, kHeadDim, 0, 1);
@@ -313,9 +366,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint64_t* const p_full = &sm.p_full[t];
         uint64_t* const pv_done = &sm.pv_done[t];
 
+        int g = 0;        // key-tile steps this query-tile slot has been through (phases of its S / P barriers)
+        int tile0 = 0;    // index of the current item's first K / V tile in the rings
+        int items_t = 0;  // items this query-tile slot has taken part in (phases of q_full, q_empty, o_free)
+        bool twice = false;  // this thread stands in for the absent second tile when it releases a ring stage
+
         // S_t(j) = Q_t K_j^T. The last key tile only computes the columns that hold keys.
         auto issue_qk = [&](int j) {
-          const int st = j % kStagesK;
+          const int st = (tile0 + j) % kStagesK;
           const uint64_t bd = k_desc0 + static_cast<uint64_t>(st) * kStageStep;
           const uint32_t idesc = (j == kv_tiles - 1) ? idesc_qk_last : idesc_qk;
 #pragma unroll
@@ -323,10 +381,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             umma_ss(s_tm, q_desc + 2 * kk, bd + 2 * kk, idesc, kk > 0 ? 1u : 0u);
           umma_commit(s_full);
           umma_commit(&sm.k_empty[st]);
+          if (twice) umma_commit(&sm.k_empty[st]);
+          if (j == kv_tiles - 1) umma_commit(&sm.q_empty[t]);  // the item's last reader of Q_t
         };
         // O_t (+)= P_t(j) V_j, 16 keys (two 8-row groups of the V tile) per step.
         auto issue_pv = [&](int j) {
-          const int st = j % kStagesV;
+          const int st = (tile0 + j) % kStagesV;
           const uint64_t bd = v_desc0 + static_cast<uint64_t>(st) * kStageStep;
           if (j != kv_tiles - 1) {
             umma_ts(o_tm, p_tm, bd, idesc_pv, j > 0 ? 1u : 0u);
@@ -340,45 +400,61 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int kk = 1; kk < kTileRows / 16; ++kk)
               if (kk < steps) umma_ts(o_tm, p_tm + kk * 8, bd + kk * (2048 >> 4), idesc_pv, 1u);
           }
-          B200_STAMP(2 + t, j, 4);
+          B200_STAMP(2 + t, g + j, 4);
           umma_commit(pv_done);
           umma_commit(&sm.v_empty[st]);
+          if (twice) umma_commit(&sm.v_empty[st]);
         };
-        auto k_ready = [&](int j) { return mbar_wait(&sm.k_full[j % kStagesK], (j / kStagesK) & 1, abort_flag); };
-        auto v_ready = [&](int j) { return mbar_wait(&sm.v_full[j % kStagesV], (j / kStagesV) & 1, abort_flag); };
+        auto k_ready = [&](int j) {
+          const int i = tile0 + j;
+          return mbar_wait(&sm.k_full[i % kStagesK], (i / kStagesK) & 1, abort_flag);
+        };
+        auto v_ready = [&](int j) {
+          const int i = tile0 + j;
+          return mbar_wait(&sm.v_full[i % kStagesV], (i / kStagesV) & 1, abort_flag);
+        };
 
-        // S_t(0), then S_t(1) as soon as S_t(0) sits in registers.
-        ok = k_ready(0) && mbar_wait(&sm.q_full[t], 0, abort_flag);
-        if (ok) {
+        for (int it = 0; it < my_items && ok; ++it, tile0 += kv_tiles) {
+          const WorkItem w = decode_item(p, blockIdx.x + it * gridDim.x);
+          if (t >= w.n_tiles) break;  // only one-tile items follow
+          twice = w.n_tiles == 1;
+
+          // S_t(0) as soon as Q, K_0 are in and the previous item's last S_t sits in registers; S_t(1) after that.
+          ok = k_ready(0) && mbar_wait(&sm.q_full[t], items_t & 1, abort_flag);
+          if (ok && g > 0) ok = mbar_wait(s_free, (g - 1) & 1, abort_flag);
+          if (!ok) break;
           tc_fence_after_sync();
           issue_qk(0);
-        }
-        if (ok && kv_tiles > 1) {
-          ok = k_ready(1) && mbar_wait(s_free, 0, abort_flag);
-          if (ok) {
+          if (kv_tiles > 1) {
+            ok = k_ready(1) && mbar_wait(s_free, g & 1, abort_flag);
+            if (!ok) break;
             tc_fence_after_sync();
             issue_qk(1);
           }
-        }
-        // Steady state: P_t(j) -> PV_t(j);  S_t(j+1) read -> QK_t(j+2).
-        for (int j = 0; j < kv_tiles && ok; ++j) {
-          const bool ahead = j + 2 < kv_tiles;
-          ok = v_ready(j) && mbar_wait(p_full, j & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after_sync();
-          B200_STAMP(2 + t, j, 0);
-          issue_pv(j);
-          B200_STAMP(2 + t, j, 1);
-          if (ahead) {
-            ok = k_ready(j + 2);
-            B200_STAMP(2 + t, j, 5);
-            ok = ok && mbar_wait(s_free, (j + 1) & 1, abort_flag);
+          // Steady state: P_t(j) -> PV_t(j);  S_t(j+1) read -> QK_t(j+2).
+          for (int j = 0; j < kv_tiles && ok; ++j) {
+            const bool ahead = j + 2 < kv_tiles;
+            ok = v_ready(j) && mbar_wait(p_full, (g + j) & 1, abort_flag);
+            // The first PV of an item overwrites O_t: the previous item's epilogue must have read it.
+            if (ok && j == 0 && items_t > 0) ok = mbar_wait(&sm.o_free[t], (items_t - 1) & 1, abort_flag);
             if (!ok) break;
             tc_fence_after_sync();
-            B200_STAMP(2 + t, j, 2);
-            issue_qk(j + 2);
-            B200_STAMP(2 + t, j, 3);
+            B200_STAMP(2 + t, g + j, 0);
+            issue_pv(j);
+            B200_STAMP(2 + t, g + j, 1);
+            if (ahead) {
+              ok = k_ready(j + 2);
+              B200_STAMP(2 + t, g + j, 5);
+              ok = ok && mbar_wait(s_free, (g + j + 1) & 1, abort_flag);
+              if (!ok) break;
+              tc_fence_after_sync();
+              B200_STAMP(2 + t, g + j, 2);
+              issue_qk(j + 2);
+              B200_STAMP(2 + t, g + j, 3);
+            }
           }
+          g += kv_tiles;
+          ++items_t;
         }
         if (!ok) {
           if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusMma);
@@ -389,20 +465,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   } else {
     // ======================= softmax warpgroups ================================================
     reg_alloc<kSoftmaxRegs>();
-    const int t = warp >> 2;  // query tile of this warpgroup
+    const int t = warp >> 2;  // query-tile slot of this warpgroup
     const int row_in_tile = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    if (t < n_tiles) {
-      const int q_row = q_row0 + t * kTileRows + row_in_tile;
+    const uint32_t s_addr = tmem + lane_addr + kTmemS + t * kTileRows;
+    const uint32_t o_addr = tmem + lane_addr + kTmemO + t * kHeadDim;
+    const uint32_t p_addr = tmem + lane_addr + kTmemP + t * kHeadDim;
+    const float c = p.scale_log2;
+    int g = 0;        // key-tile steps of this slot so far (phases of s_full, s_free, p_full, pv_done)
+    int gp = 0;       // steps so far in items where both warpgroups work (phases of the turn barriers)
+    bool ok = true;
+
+    for (int it = 0; it < my_items && ok; ++it) {
+      const WorkItem w = decode_item(p, blockIdx.x + it * gridDim.x);
+      if (t >= w.n_tiles) break;  // only one-tile items follow
+      const int b = w.b, h = w.h;
+      const int q_row = w.q_row0 + t * kTileRows + row_in_tile;
       const bool row_valid = q_row < p.q_tokens;
-      const uint32_t s_addr = tmem + lane_addr + kTmemS + t * kTileRows;
-      const uint32_t o_addr = tmem + lane_addr + kTmemO + t * kHeadDim;
-      const uint32_t p_addr = tmem + lane_addr + kTmemP + t * kHeadDim;
-      const float c = p.scale_log2;
-      const bool pingpong = n_tiles == 2 && !(p.flags & 1);
+      const bool pingpong = w.n_tiles == 2 && !(p.flags & 1);
       float m_ref = -INFINITY;
       float l_sum = 0.f;
-      bool ok = true;
 
       int64_t bias_row = 0, bias2_row = 0;
       if constexpr (BIAS != kBiasNone) {
@@ -412,10 +494,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
 
       for (int j = 0; j < kv_tiles; ++j) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_full[t], j & 1, abort_flag));
+        const int step = g + j;
+        ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_full[t], step & 1, abort_flag));
         if (!ok) break;
         tc_fence_after_sync();
-        if ((warp & 3) == 0) B200_STAMP(t, j, 0);
+        if ((warp & 3) == 0) B200_STAMP(t, step, 0);
 
         float s[kTileRows];
         {
@@ -426,7 +509,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // S_t is in registers: the tensor pipe may overwrite it with the tile after next.
         tc_fence_before_sync();
         warp_arrive(&sm.s_free[t], lane);
-        if ((warp & 3) == 0) B200_STAMP(t, j, 1);
+        if ((warp & 3) == 0) B200_STAMP(t, step, 1);
 
         const int kv0 = j * kTileRows;
         const int kv_valid = min(kTileRows, p.kv_tokens - kv0);
@@ -482,21 +565,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         l_sum *= alpha;
         const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-
-        if ((warp & 3) == 0) B200_STAMP(t, j, 6);
+        if ((warp & 3) == 0) B200_STAMP(t, step, 6);
 
         // ---- exponentials ---------------------------------------------------------------------------
         // Both warpgroups feed the MUFU unit, but they must not run in lockstep (their loads and reductions
         // would leave the unit idle together, and equal loops sharing a unit drift into lockstep). So each
         // may only start a section once the other is half way through its previous one: warpgroup 0 starts
-        // tile j+1 after warpgroup 1's midpoint of tile j, warpgroup 1 starts tile j after warpgroup 0's
-        // midpoint of tile j. Half a section apart, neither ever waits here.
-        if (pingpong && (t == 1 || j > 0)) {
-          const uint32_t parity = (t == 0) ? ((j - 1) & 1) : (j & 1);
+        // step q+1 after warpgroup 1's midpoint of step q, warpgroup 1 starts step q after warpgroup 0's
+        // midpoint of step q. Half a section apart, neither ever waits here.
+        if (pingpong && (t == 1 || gp + j > 0)) {
+          const uint32_t parity = (t == 0) ? ((gp + j - 1) & 1) : ((gp + j) & 1);
           ok = __all_sync(0xffffffffu, mbar_wait(&sm.turn[t], parity, abort_flag));
           if (!ok) break;
         }
-        if ((warp & 3) == 0) B200_STAMP(t, j, 2);
+        if ((warp & 3) == 0) B200_STAMP(t, step, 2);
         float2 l2a = make_float2(0.f, 0.f), l2b = make_float2(0.f, 0.f);
         const float2 c2 = (BIAS == kBiasNone) ? make_float2(c, c) : make_float2(1.f, 1.f);
         float nm = -m_use;
@@ -518,13 +600,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // Midpoint: let the other warpgroup start. The second half reads `nm` through the arrival.
           if (half == 0 && pingpong) warp_arrive_pinned(&sm.turn[t ^ 1], lane, nm);
         }
-        if ((warp & 3) == 0) B200_STAMP(t, j, 3);
+        if ((warp & 3) == 0) B200_STAMP(t, step, 3);
         l_sum += (l2a.x + l2a.y) + (l2b.x + l2b.y);
 
         // P_t and O_t may only change once P_t(j-1) V has finished: it was issued when this warpgroup
-        // delivered P_t(j-1), a whole exponential section ago.
+        // delivered P_t(j-1), a whole exponential section ago. (For j = 0 the previous item's epilogue
+        // has already waited for its last P V.)
         if (j > 0) {
-          ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done[t], (j - 1) & 1, abort_flag));
+          ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done[t], (step - 1) & 1, abort_flag));
           if (!ok) break;
           tc_fence_after_sync();
           if (__any_sync(0xffffffffu, raise)) {
@@ -537,36 +620,42 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tmem_st_x32(o_addr + 32, ou + 32);
           }
         }
-        if ((warp & 3) == 0) B200_STAMP(t, j, 4);
+        if ((warp & 3) == 0) B200_STAMP(t, step, 4);
         tmem_st_x32(p_addr, pk);
         tmem_st_x32(p_addr + 32, pk + 32);
         tmem_st_wait();
         tc_fence_before_sync();
         warp_arrive(&sm.p_full[t], lane);
-        if ((warp & 3) == 0) B200_STAMP(t, j, 5);
+        if ((warp & 3) == 0) B200_STAMP(t, step, 5);
       }
+      if (!ok) break;
 
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done[t], (kv_tiles - 1) & 1, abort_flag));
-      if (ok) {
-        tc_fence_after_sync();
-        float o[kHeadDim];
-        tmem_ld_x64(o_addr, reinterpret_cast<uint32_t*>(o));
-        if (row_valid) {
-          const float inv = 1.f / l_sum;
-          T* dst = reinterpret_cast<T*>(p.o) + b * p.o_sb + static_cast<int64_t>(q_row) * p.o_sn + h * p.o_sh;
+      // ---- epilogue of the item: O_t / l -> global ----------------------------------------------------
+      ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done[t], (g + kv_tiles - 1) & 1, abort_flag));
+      if (!ok) break;
+      tc_fence_after_sync();
+      float o[kHeadDim];
+      tmem_ld_x64(o_addr, reinterpret_cast<uint32_t*>(o));
+      tc_fence_before_sync();
+      warp_arrive(&sm.o_free[t], lane);  // the next item's first P V may overwrite O_t
+      if (row_valid) {
+        const float inv = 1.f / l_sum;
+        T* dst = reinterpret_cast<T*>(p.o) + b * p.o_sb + static_cast<int64_t>(q_row) * p.o_sn + h * p.o_sh;
 #pragma unroll
-          for (int ch = 0; ch < kHeadDim / 8; ++ch) {
-            uint4 val;
-            val.x = pack2<T>(o[ch * 8 + 0] * inv, o[ch * 8 + 1] * inv);
-            val.y = pack2<T>(o[ch * 8 + 2] * inv, o[ch * 8 + 3] * inv);
-            val.z = pack2<T>(o[ch * 8 + 4] * inv, o[ch * 8 + 5] * inv);
-            val.w = pack2<T>(o[ch * 8 + 6] * inv, o[ch * 8 + 7] * inv);
-            *reinterpret_cast<uint4*>(dst + ch * 8) = val;
-          }
+        for (int ch = 0; ch < kHeadDim / 8; ++ch) {
+          uint4 val;
+          val.x = pack2<T>(o[ch * 8 + 0] * inv, o[ch * 8 + 1] * inv);
+          val.y = pack2<T>(o[ch * 8 + 2] * inv, o[ch * 8 + 3] * inv);
+          val.z = pack2<T>(o[ch * 8 + 4] * inv, o[ch * 8 + 5] * inv);
+          val.w = pack2<T>(o[ch * 8 + 6] * inv, o[ch * 8 + 7] * inv);
+          *reinterpret_cast<uint4*>(dst + ch * 8) = val;
         }
-      } else if (lane == 0) {
-        if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusSoftmax);
       }
+      g += kv_tiles;
+      if (w.n_tiles == 2) gp += kv_tiles;
+    }
+    if (!ok && lane == 0) {
+      if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusSoftmax);
     }
   }
 

@@ -168,7 +168,13 @@ int launch(const B200AttnArgs* a, const AttnParams& prm, const CUtensorMap& mq, 
   // The opt-in is per device and per kernel; setting it again is cheap and keeps this path stateless.
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(shared memory)");
-  const unsigned grid = static_cast<unsigned>(prm.items_per_head) * a->batch * a->heads;
+  // Persistent CTAs: one per SM (shared memory and tensor memory allow no more), fewer when there is less work.
+  int device = 0, sms = 0;
+  e = cudaGetDevice(&device);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(multiprocessor count)");
+  const long long items = static_cast<long long>(prm.items_per_head) * a->batch * a->heads;
+  const unsigned grid = static_cast<unsigned>(items < sms ? items : sms);
   kernel<<<grid, kThreads, smem, stream>>>(mq, mk, mv, prm);
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "attention kernel launch");
@@ -203,7 +209,8 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
   prm.heads = a->heads;
   prm.q_tokens = a->q_tokens;
   prm.kv_tokens = a->kv_tokens;
-  prm.items_per_head = (a->q_tokens + 2 * kTileRows - 1) / (2 * kTileRows);
+  prm.q_tiles = (a->q_tokens + kTileRows - 1) / kTileRows;
+  prm.items_per_head = (prm.q_tiles + 1) / 2;
   prm.kv_tiles = (a->kv_tokens + kTileRows - 1) / kTileRows;
   prm.scale_log2 = a->scale * kLog2e;
   prm.o = a->o;

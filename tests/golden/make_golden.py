@@ -102,6 +102,28 @@ def sam_case(seed: int, b: int, hw: tuple[int, int], dim: int, heads: int, std: 
     }  # fmt: skip
 
 
+def dinov2_model_case(seed: int, name: str, hw: tuple[int, int], qk_gain: float) -> dict[str, np.ndarray]:
+    """The reference's vendored DINOv2 network (portable fp32, CPU) on the seeded weights of
+    `fastforks_b200.vit.seeded_state`, loaded strictly: the harness and the reference share one parameterisation.
+    Only the input seed and the output are stored; the weights are regenerated from the seed."""
+    sys.path.insert(0, str(HERE.parent.parent))
+    from fastforks.shared.depth_anything_v2 import DINOv2
+
+    from fastforks_b200.vit import CONFIGS, seeded_state
+
+    cfg = CONFIGS[name]
+    net = DINOv2({"dinov2-vits14": "vits", "dinov2-vitb14": "vitb"}[name]).eval()
+    state = seeded_state(cfg, seed, qk_gain=qk_gain)
+    assert list(net.state_dict()) == list(state), "parameter names / order differ from the reference network"
+    net.load_state_dict(state, strict=True)
+    images = torch.rand(1, 3, *hw, generator=torch.Generator().manual_seed(seed + 1))
+    with torch.no_grad():
+        feats = net.forward_features(images)
+    tokens = torch.cat([feats["x_norm_clstoken"][:, None], feats["x_norm_patchtokens"]], 1)
+    return {"out": tokens, "seed": np.int64(seed), "image_seed": np.int64(seed + 1), "hw": np.array(hw, dtype=np.int32),
+            "qk_gain": np.float32(qk_gain)}  # fmt: skip
+
+
 CASES = {
     # name: (builder, kwargs). Token counts follow the reference: 97 = its feature-golden input (112x168, patch 14),
     # 197 = ViT-B/16 at 224, 196 = one 14x14 SAM window; 8x16 exercises kh != kw.
@@ -110,6 +132,9 @@ CASES = {
     "timm_n197": (timm_case, {"seed": 2, "b": 1, "n": 197, "dim": 128, "heads": 2, "std": 0.08}),
     "sam_window_14x14": (sam_case, {"seed": 3, "b": 1, "hw": (14, 14), "dim": 128, "heads": 2, "std": 0.08}),
     "sam_grid_8x16": (sam_case, {"seed": 4, "b": 2, "hw": (8, 16), "dim": 64, "heads": 1, "std": 0.1}),
+    # whole encoder, N = 1 + 16 * 12 = 193 tokens (a non-square grid exercises the position interpolation)
+    "model_dinov2_vits14": (dinov2_model_case, {"seed": 7, "name": "dinov2-vits14", "hw": (224, 168), "qk_gain": 1.0}),
+    "model_dinov2_vits14_sharp": (dinov2_model_case, {"seed": 8, "name": "dinov2-vits14", "hw": (224, 224), "qk_gain": 8.0}),
 }
 
 
