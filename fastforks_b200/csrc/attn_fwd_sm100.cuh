@@ -42,7 +42,7 @@ constexpr int kLaunchRegs = 168;                      // what a 384-thread CTA g
 // allocated, or the second warpgroup waits for ever.
 static_assert(2 * 128 * kSoftmaxRegs + 128 * kHelperRegs <= kLaunchRegs * kThreads,
               "register hand-over does not balance");
-constexpr int kStagesK = 4, kStagesV = 4;
+constexpr int kStagesK = 3, kStagesV = 3;
 constexpr int kKLead = 2;                             // K tiles are consumed two iterations ahead of V tiles
 constexpr uint32_t kTmemCols = 512;                   // S0 S1 (128 each), O0 O1 (64 each), P0 P1 (64 each)
 constexpr uint32_t kTmemS = 0, kTmemO = 256, kTmemP = 384;
@@ -67,7 +67,10 @@ enum : uint32_t { kStatusLoader = 1, kStatusMma = 2, kStatusSoftmax = 4 };
   do {                               \
   } while (0)
 #endif
-enum : int { kBiasNone = 0, kBiasDense = 1, kBiasDecomposed = 2 };
+// Bias forms. kBiasDecomposed64 is the decomposed form specialised for rel_kw == 64 with 16-bit, 16-byte aligned
+// rel_w rows (SAM's global layers): a key tile then spans exactly two rel_h entries and the whole rel_w row twice.
+enum : int { kBiasNone = 0, kBiasDense = 1, kBiasDecomposed = 2, kBiasDecomposed64 = 3 };
+constexpr int kRelStageWords = 33;  // per-row staging of rel_h | rel_w in shared memory: up to 32 values, odd stride
 
 struct BiasView {
   const void* ptr;
@@ -85,18 +88,19 @@ struct AttnParams {
   int64_t o_sb, o_sn, o_sh;
   BiasView bias;       // dense bias, or rel_h of the decomposed form
   BiasView bias2;      // rel_w of the decomposed form
-  int rel_kw;
+  int rel_kh, rel_kw;
+  int rel_staged;      // decomposed form: rel_kh + rel_kw <= 32, rows are staged in shared memory per item
+  int bias_vec;        // dense form: rows are 16-byte aligned, full tiles are read with vector loads
   uint32_t* status;    // device word that collects role bits of expired waits
   long long* trace;    // development builds only (B200_TRACE), else unused
-  int flags;           // development knobs
 };
 
 struct alignas(1024) AttnSmem {
-  uint8_t q[2][kTileBytes];
+  uint8_t q[2][2][kTileBytes];  // [query-tile slot][item parity]: the next item's Q is loaded while this one computes
   uint8_t k[kStagesK][kTileBytes];
   uint8_t v[kStagesV][kTileBytes];
-  uint64_t q_full[2];   // Q_t of the current item has landed                (TMA)
-  uint64_t q_empty[2];  // the item's last Q_t K^T has finished               (MMA commit)
+  uint64_t q_full[2][2];   // Q_t of an item has landed                      (TMA)
+  uint64_t q_empty[2][2];  // that item's last Q_t K^T has finished          (MMA commit)
   uint64_t k_full[kStagesK], k_empty[kStagesK];
   uint64_t v_full[kStagesV], v_empty[kStagesV];
   uint64_t s_full[2];   // S_t(j) is in tensor memory                     (MMA commit)
@@ -107,6 +111,7 @@ struct alignas(1024) AttnSmem {
   uint64_t turn[2];     // the other warpgroup is half way through its exponentials: t may start (4 warps)
   uint32_t tmem_base;
   uint32_t abort;
+  float rel_stage[2][kTileRows][kRelStageWords];  // each softmax thread's own rel_h | rel_w row, times log2(e)
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -151,17 +156,6 @@ __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
   return d;
 }
 
-// Spins for `clocks` SM cycles. A tcgen05.mma that finds the tensor pipe's queue full stalls at dispatch and
-// takes the issue port of its SM sub-partition with it, which starves the softmax warps that live there; an issuer
-// that waits out the previous MMA before sending the next one never hits a full queue.
-__device__ __forceinline__ void pace(long long& last, int clocks) {
-  long long now;
-  do {
-    asm volatile("mov.u64 %0, %%clock64;" : "=l"(now));
-  } while (now - last < clocks);
-  last = now;
-}
-
 // One arrival for the whole warp, after all its lanes have reached this point.
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   __syncwarp();
@@ -194,6 +188,12 @@ template <>
 __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Two packed 16-bit values (fp16 when `is_half`, else bf16) as floats.
+__device__ __forceinline__ float2 unpack2(uint32_t v, bool is_half) {
+  if (is_half) return __half22float2(*reinterpret_cast<const __half2*>(&v));
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
 }
 
 __device__ __forceinline__ float load_bias_elem(const void* base, int dtype, int64_t idx) {
@@ -254,8 +254,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // ---- set-up: barriers, tensor memory -------------------------------------------------------
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&sm.q_full[i], 1);
-      mbar_init(&sm.q_empty[i], 1);
+      for (int k = 0; k < 2; ++k) {
+        mbar_init(&sm.q_full[i][k], 1);
+        mbar_init(&sm.q_empty[i][k], 1);
+      }
       mbar_init(&sm.s_full[i], 1);
       mbar_init(&sm.s_free[i], 4);  // one arrival per softmax warp: 128 arrivals on one word take hundreds of clocks
       mbar_init(&sm.p_full[i], 4);
@@ -299,17 +301,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         int q_count[2] = {0, 0};   // Q tiles issued so far per query-tile slot
         for (int it = 0; it < my_items && ok; ++it) {
           const WorkItem w = decode_item(p, blockIdx.x + it * gridDim.x);
+          const int slot = it & 1;
           for (int t = 0; t < w.n_tiles && ok; ++t) {
-            if (q_count[t] > 0) ok = mbar_wait(&sm.q_empty[t], (q_count[t] - 1) & 1, abort_flag);
+            ok = mbar_wait_relaxed(&sm.q_empty[t][slot], ((it >> 1) & 1) ^ 1, abort_flag);
             if (!ok) break;
-            mbar_arrive_expect_tx(&sm.q_full[t], kTileBytes);
-            tma_load_4d(sm.q[t], &tm_q, &sm.q_full[t], 0, w.q_row0 + t * kTileRows, w.h, w.b);
-            ++q_count[t];
+            mbar_arrive_expect_tx(&sm.q_full[t][slot], kTileBytes);
+            tma_load_4d(sm.q[t][slot], &tm_q, &sm.q_full[t][slot], 0, w.q_row0 + t * kTileRows, w.h, w.b);
+            q_count[t] = it + 1;
           }
           for (int i = 0; i < kv_tiles + kKLead && ok; ++i) {
             if (i < kv_tiles) {
               const int st = gk % kStagesK;
-              ok = mbar_wait(&sm.k_empty[st], ((gk / kStagesK) & 1) ^ 1, abort_flag);
+              ok = mbar_wait_relaxed(&sm.k_empty[st], ((gk / kStagesK) & 1) ^ 1, abort_flag);
               if (!ok) break;
               mbar_arrive_expect_tx(&sm.k_full[st], kTileBytes);
               tma_load_4d(sm.k[st], &tm_k, &sm.k_full[st], 0, i * kTileRows, w.h, w.b);
@@ -318,7 +321,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const int jv = i - kKLead;
             if (jv >= 0) {
               const int st = gv % kStagesV;
-              ok = mbar_wait(&sm.v_empty[st], ((gv / kStagesV) & 1) ^ 1, abort_flag);
+              ok = mbar_wait_relaxed(&sm.v_empty[st], ((gv / kStagesV) & 1) ^ 1, abort_flag);
               if (!ok) break;
               mbar_arrive_expect_tx(&sm.v_full[st], kTileBytes);
               tma_load_4d(sm.v[st], &tm_v, &sm.v_full[st], 0, jv * kTileRows, w.h, w.b);
@@ -334,11 +337,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // that was issued, so that none writes into shared memory after the CTA has gone.
           uint32_t no_abort = 0;
           for (int t = 0; t < 2; ++t)
-            if (q_count[t] > 0) mbar_wait(&sm.q_full[t], (q_count[t] - 1) & 1, &no_abort);
+            for (int i = (q_count[t] > 2 ? q_count[t] - 2 : 0); i < q_count[t]; ++i)
+              mbar_wait_relaxed(&sm.q_full[t][i & 1], (i >> 1) & 1, &no_abort);
           for (int j = (gk > kStagesK ? gk - kStagesK : 0); j < gk; ++j)
-            mbar_wait(&sm.k_full[j % kStagesK], (j / kStagesK) & 1, &no_abort);
+            mbar_wait_relaxed(&sm.k_full[j % kStagesK], (j / kStagesK) & 1, &no_abort);
           for (int j = (gv > kStagesV ? gv - kStagesV : 0); j < gv; ++j)
-            mbar_wait(&sm.v_full[j % kStagesV], (j / kStagesV) & 1, &no_abort);
+            mbar_wait_relaxed(&sm.v_full[j % kStagesV], (j / kStagesV) & 1, &no_abort);
         }
       }
       __syncwarp();
@@ -354,10 +358,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
         // Everything the issue loops need is computed once: one thread feeds the tensor pipe, and every
         // instruction between two tcgen05.mma shows up as an idle pipe when the MMAs are this small.
-        const uint64_t q_desc = umma_smem_desc_sw128(smem_u32(sm.q[t]), 1024, 16);
+        const uint64_t q_desc0 = umma_smem_desc_sw128(smem_u32(sm.q[t][0]), 1024, 16);
         const uint64_t k_desc0 = umma_smem_desc_sw128(smem_u32(sm.k[0]), 1024, 16);
         const uint64_t v_desc0 = umma_smem_desc_sw128(smem_u32(sm.v[0]), 1024, 0);
-        constexpr uint64_t kStageStep = kTileBytes >> 4;  // descriptor distance between two ring stages
+        constexpr uint64_t kStageStep = kTileBytes >> 4;  // descriptor distance between two tiles in shared memory
         const uint32_t s_tm = tmem + kTmemS + t * kTileRows;
         const uint32_t o_tm = tmem + kTmemO + t * kHeadDim;
         const uint32_t p_tm = tmem + kTmemP + t * kHeadDim;
@@ -366,27 +370,43 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint64_t* const p_full = &sm.p_full[t];
         uint64_t* const pv_done = &sm.pv_done[t];
 
-        int g = 0;        // key-tile steps this query-tile slot has been through (phases of its S / P barriers)
-        int tile0 = 0;    // index of the current item's first K / V tile in the rings
-        int items_t = 0;  // items this query-tile slot has taken part in (phases of q_full, q_empty, o_free)
-        bool twice = false;  // this thread stands in for the absent second tile when it releases a ring stage
+        // This slot's items are a prefix of the CTA's list (two-tile items come first), so its key-tile steps form
+        // one stream gs = 0, 1, ...: step gs is tile gs % kv_tiles of item gs / kv_tiles and uses ring tile gs.
+        // S is issued two steps ahead of its use, across item boundaries too, so that a new item starts at once.
+        const int total_doubles = (p.q_tiles >> 1) * p.batch * p.heads;
+        int my_doubles = (total_doubles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                         static_cast<int>(gridDim.x);
+        my_doubles = my_doubles < 0 ? 0 : (my_doubles > my_items ? my_items : my_doubles);
+        const int total_steps = (t == 0 ? my_items : my_doubles) * kv_tiles;
 
-        // S_t(j) = Q_t K_j^T. The last key tile only computes the columns that hold keys.
-        auto issue_qk = [&](int j) {
-          const int st = (tile0 + j) % kStagesK;
+        // S_t(gs) = Q_t K^T. The last key tile of an item only computes the columns that hold keys.
+        auto issue_qk = [&](int gs) -> bool {
+          const int it = gs / kv_tiles, j = gs - it * kv_tiles, slot = it & 1, st = gs % kStagesK;
+          if (!mbar_wait_relaxed(&sm.k_full[st], (gs / kStagesK) & 1, abort_flag)) return false;
+          if (j == 0 && !mbar_wait_relaxed(&sm.q_full[t][slot], (it >> 1) & 1, abort_flag)) return false;
+          if (gs > 0 && !mbar_wait_relaxed(s_free, (gs - 1) & 1, abort_flag)) return false;  // S_t has been read
+          tc_fence_after_sync();
+          const uint64_t a = q_desc0 + static_cast<uint64_t>(slot) * kStageStep;
           const uint64_t bd = k_desc0 + static_cast<uint64_t>(st) * kStageStep;
           const uint32_t idesc = (j == kv_tiles - 1) ? idesc_qk_last : idesc_qk;
 #pragma unroll
           for (int kk = 0; kk < kHeadDim / 16; ++kk)  // 32 bytes of K per step inside the swizzle atom
-            umma_ss(s_tm, q_desc + 2 * kk, bd + 2 * kk, idesc, kk > 0 ? 1u : 0u);
+            umma_ss(s_tm, a + 2 * kk, bd + 2 * kk, idesc, kk > 0 ? 1u : 0u);
           umma_commit(s_full);
           umma_commit(&sm.k_empty[st]);
-          if (twice) umma_commit(&sm.k_empty[st]);
-          if (j == kv_tiles - 1) umma_commit(&sm.q_empty[t]);  // the item's last reader of Q_t
+          if (it >= my_doubles) umma_commit(&sm.k_empty[st]);  // one-tile item: stand in for the absent second tile
+          if (j == kv_tiles - 1) umma_commit(&sm.q_empty[t][slot]);  // the item's last reader of Q_t
+          return true;
         };
-        // O_t (+)= P_t(j) V_j, 16 keys (two 8-row groups of the V tile) per step.
-        auto issue_pv = [&](int j) {
-          const int st = (tile0 + j) % kStagesV;
+        // O_t (+)= P_t(gs) V, 16 keys (two 8-row groups of the V tile) per MMA.
+        auto issue_pv = [&](int gs) -> bool {
+          const int it = gs / kv_tiles, j = gs - it * kv_tiles, st = gs % kStagesV;
+          if (!mbar_wait_relaxed(&sm.v_full[st], (gs / kStagesV) & 1, abort_flag)) return false;
+          if (!mbar_wait_relaxed(p_full, gs & 1, abort_flag)) return false;
+          // The first P V of an item overwrites O_t: the previous item's epilogue must have read it.
+          if (j == 0 && it > 0 && !mbar_wait_relaxed(&sm.o_free[t], (it - 1) & 1, abort_flag)) return false;
+          tc_fence_after_sync();
+          B200_STAMP(2 + t, gs, 0);
           const uint64_t bd = v_desc0 + static_cast<uint64_t>(st) * kStageStep;
           if (j != kv_tiles - 1) {
             umma_ts(o_tm, p_tm, bd, idesc_pv, j > 0 ? 1u : 0u);
@@ -400,61 +420,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int kk = 1; kk < kTileRows / 16; ++kk)
               if (kk < steps) umma_ts(o_tm, p_tm + kk * 8, bd + kk * (2048 >> 4), idesc_pv, 1u);
           }
-          B200_STAMP(2 + t, g + j, 4);
           umma_commit(pv_done);
           umma_commit(&sm.v_empty[st]);
-          if (twice) umma_commit(&sm.v_empty[st]);
-        };
-        auto k_ready = [&](int j) {
-          const int i = tile0 + j;
-          return mbar_wait(&sm.k_full[i % kStagesK], (i / kStagesK) & 1, abort_flag);
-        };
-        auto v_ready = [&](int j) {
-          const int i = tile0 + j;
-          return mbar_wait(&sm.v_full[i % kStagesV], (i / kStagesV) & 1, abort_flag);
+          if (it >= my_doubles) umma_commit(&sm.v_empty[st]);
+          B200_STAMP(2 + t, gs, 1);
+          return true;
         };
 
-        for (int it = 0; it < my_items && ok; ++it, tile0 += kv_tiles) {
-          const WorkItem w = decode_item(p, blockIdx.x + it * gridDim.x);
-          if (t >= w.n_tiles) break;  // only one-tile items follow
-          twice = w.n_tiles == 1;
-
-          // S_t(0) as soon as Q, K_0 are in and the previous item's last S_t sits in registers; S_t(1) after that.
-          ok = k_ready(0) && mbar_wait(&sm.q_full[t], items_t & 1, abort_flag);
-          if (ok && g > 0) ok = mbar_wait(s_free, (g - 1) & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after_sync();
-          issue_qk(0);
-          if (kv_tiles > 1) {
-            ok = k_ready(1) && mbar_wait(s_free, g & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after_sync();
-            issue_qk(1);
-          }
-          // Steady state: P_t(j) -> PV_t(j);  S_t(j+1) read -> QK_t(j+2).
-          for (int j = 0; j < kv_tiles && ok; ++j) {
-            const bool ahead = j + 2 < kv_tiles;
-            ok = v_ready(j) && mbar_wait(p_full, (g + j) & 1, abort_flag);
-            // The first PV of an item overwrites O_t: the previous item's epilogue must have read it.
-            if (ok && j == 0 && items_t > 0) ok = mbar_wait(&sm.o_free[t], (items_t - 1) & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after_sync();
-            B200_STAMP(2 + t, g + j, 0);
-            issue_pv(j);
-            B200_STAMP(2 + t, g + j, 1);
-            if (ahead) {
-              ok = k_ready(j + 2);
-              B200_STAMP(2 + t, g + j, 5);
-              ok = ok && mbar_wait(s_free, (g + j + 1) & 1, abort_flag);
-              if (!ok) break;
-              tc_fence_after_sync();
-              B200_STAMP(2 + t, g + j, 2);
-              issue_qk(j + 2);
-              B200_STAMP(2 + t, g + j, 3);
-            }
-          }
-          g += kv_tiles;
-          ++items_t;
+        if (total_steps > 0) ok = issue_qk(0);
+        if (ok && total_steps > 1) ok = issue_qk(1);
+        for (int gs = 0; gs < total_steps && ok; ++gs) {
+          ok = issue_pv(gs);
+          if (ok && gs + 2 < total_steps) ok = issue_qk(gs + 2);
         }
         if (!ok) {
           if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusMma);
@@ -475,6 +452,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     int g = 0;        // key-tile steps of this slot so far (phases of s_full, s_free, p_full, pv_done)
     int gp = 0;       // steps so far in items where both warpgroups work (phases of the turn barriers)
     bool ok = true;
+    // Epilogue of the previous item, still to be done: its last P V phase, 1 / row sum, output row (or null).
+    bool pend = false;
+    uint32_t pend_phase = 0;
+    float pend_inv = 0.f;
+    T* pend_dst = nullptr;
+    // O_t / l -> global for the pending item; frees O_t for the next item's first P V.
+    auto finish_item = [&]() -> bool {
+      if (!__all_sync(0xffffffffu, mbar_wait(&sm.pv_done[t], pend_phase, abort_flag))) return false;
+      tc_fence_after_sync();
+      float o[kHeadDim];
+      tmem_ld_x64(o_addr, reinterpret_cast<uint32_t*>(o));
+      tc_fence_before_sync();
+      warp_arrive(&sm.o_free[t], lane);
+      if (pend_dst != nullptr) {
+#pragma unroll
+        for (int ch = 0; ch < kHeadDim / 8; ++ch) {
+          uint4 val;
+          val.x = pack2<T>(o[ch * 8 + 0] * pend_inv, o[ch * 8 + 1] * pend_inv);
+          val.y = pack2<T>(o[ch * 8 + 2] * pend_inv, o[ch * 8 + 3] * pend_inv);
+          val.z = pack2<T>(o[ch * 8 + 4] * pend_inv, o[ch * 8 + 5] * pend_inv);
+          val.w = pack2<T>(o[ch * 8 + 6] * pend_inv, o[ch * 8 + 7] * pend_inv);
+          *reinterpret_cast<uint4*>(pend_dst + ch * 8) = val;
+        }
+      }
+      pend = false;
+      return true;
+    };
 
     for (int it = 0; it < my_items && ok; ++it) {
       const WorkItem w = decode_item(p, blockIdx.x + it * gridDim.x);
@@ -482,7 +486,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int b = w.b, h = w.h;
       const int q_row = w.q_row0 + t * kTileRows + row_in_tile;
       const bool row_valid = q_row < p.q_tokens;
-      const bool pingpong = w.n_tiles == 2 && !(p.flags & 1);
+      const bool pingpong = w.n_tiles == 2;
       float m_ref = -INFINITY;
       float l_sum = 0.f;
 
@@ -490,7 +494,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if constexpr (BIAS != kBiasNone) {
         const int qr = row_valid ? q_row : 0;
         bias_row = b * p.bias.sb + h * p.bias.sh + qr * p.bias.sn;
-        if constexpr (BIAS == kBiasDecomposed) bias2_row = b * p.bias2.sb + h * p.bias2.sh + qr * p.bias2.sn;
+        if constexpr (BIAS == kBiasDecomposed || BIAS == kBiasDecomposed64)
+          bias2_row = b * p.bias2.sb + h * p.bias2.sh + qr * p.bias2.sn;
+        if constexpr (BIAS == kBiasDecomposed) {
+          if (p.rel_staged) {  // this thread's rows, read back by this thread only: no synchronisation needed
+            float* stage = sm.rel_stage[t][row_in_tile];
+            float tmp[kRelStageWords - 1];
+#pragma unroll
+            for (int i = 0; i < kRelStageWords - 1; ++i) {  // all loads in flight together
+              const bool in_h = i < p.rel_kh;
+              const bool in_w = !in_h && i < p.rel_kh + p.rel_kw;
+              tmp[i] = in_h   ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + i)
+                       : in_w ? load_bias_elem(p.bias2.ptr, p.bias2.dtype, bias2_row + (i - p.rel_kh))
+                              : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < kRelStageWords - 1; ++i) stage[i] = tmp[i] * kLog2e;
+          }
+        }
       }
 
       for (int j = 0; j < kv_tiles; ++j) {
@@ -515,24 +536,88 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int kv_valid = min(kTileRows, p.kv_tokens - kv0);
 
         if constexpr (BIAS == kBiasDense) {
+          if (p.bias_vec && kv_valid == kTileRows && p.bias.dtype != 2) {
+            // 16-bit bias, aligned rows, full tile: 32 columns (four 16-byte loads) at a time
+            const bool is_half = p.bias.dtype == 0;
+            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias.ptr) + bias_row + kv0);
 #pragma unroll
-          for (int i = 0; i < kTileRows; ++i) {
-            const float bv = (i < kv_valid) ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + kv0 + i) : 0.f;
-            s[i] = fmaf(s[i], c, bv * kLog2e);
+            for (int ch = 0; ch < 4; ++ch) {
+              uint4 v[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) v[u] = __ldg(src + ch * 4 + u);
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const uint32_t w4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 bv = unpack2(w4[e], is_half);
+                  const int i = ch * 32 + u * 8 + e * 2;
+                  s[i] = fmaf(s[i], c, bv.x * kLog2e);
+                  s[i + 1] = fmaf(s[i + 1], c, bv.y * kLog2e);
+                }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < kTileRows; ++i) {
+              const float bv = (i < kv_valid) ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + kv0 + i) : 0.f;
+              s[i] = fmaf(s[i], c, bv * kLog2e);
+            }
+          }
+        } else if constexpr (BIAS == kBiasDecomposed64) {
+          // Keys kv0 .. kv0+127 are (row 2j, all 64 columns) then (row 2j+1, all 64 columns) of the key grid.
+          const bool is_half = p.bias2.dtype == 0;
+          const int ih = kv0 >> 6;
+          const float rh0 = load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih) * kLog2e;
+          const float rh1 = (ih + 1 < p.rel_kh) ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih + 1) * kLog2e : 0.f;
+          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias2.ptr) + bias2_row);
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch) {  // 32 rel_w values at a time, used by columns ch*32.. and 64+ch*32..
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = __ldg(src + ch * 4 + u);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const uint32_t w4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 rw = unpack2(w4[e], is_half);
+                const int i = ch * 32 + u * 8 + e * 2;
+                s[i] = fmaf(s[i], c, fmaf(rw.x, kLog2e, rh0));
+                s[i + 1] = fmaf(s[i + 1], c, fmaf(rw.y, kLog2e, rh0));
+                s[i + 64] = fmaf(s[i + 64], c, fmaf(rw.x, kLog2e, rh1));
+                s[i + 65] = fmaf(s[i + 65], c, fmaf(rw.y, kLog2e, rh1));
+              }
+            }
           }
         } else if constexpr (BIAS == kBiasDecomposed) {
           int ih = kv0 / p.rel_kw;
           int iw = kv0 - ih * p.rel_kw;
-          float bh_val = load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih);
+          if (p.rel_staged) {
+            const float* rh = sm.rel_stage[t][row_in_tile];
+            const float* rw = rh + p.rel_kh;
+            float bh_val = rh[ih];
 #pragma unroll
-          for (int i = 0; i < kTileRows; ++i) {
-            float bv = 0.f;
-            if (i < kv_valid) bv = bh_val + load_bias_elem(p.bias2.ptr, p.bias2.dtype, bias2_row + iw);
-            s[i] = fmaf(s[i], c, bv * kLog2e);
-            if (++iw == p.rel_kw) {
-              iw = 0;
-              ++ih;
-              if (i + 1 < kv_valid) bh_val = load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih);
+            for (int i = 0; i < kTileRows; ++i) {
+              if (i < kv_valid) s[i] = fmaf(s[i], c, bh_val + rw[iw]);
+              if (++iw == p.rel_kw) {
+                iw = 0;
+                ++ih;
+                if (i + 1 < kv_valid) bh_val = rh[ih];
+              }
+            }
+          } else {
+            float bh_val = load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih);
+#pragma unroll
+            for (int i = 0; i < kTileRows; ++i) {
+              float bv = 0.f;
+              if (i < kv_valid) bv = bh_val + load_bias_elem(p.bias2.ptr, p.bias2.dtype, bias2_row + iw);
+              s[i] = fmaf(s[i], c, bv * kLog2e);
+              if (++iw == p.rel_kw) {
+                iw = 0;
+                ++ih;
+                if (i + 1 < kv_valid) bh_val = load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih);
+              }
             }
           }
         }
@@ -604,9 +689,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         l_sum += (l2a.x + l2a.y) + (l2b.x + l2b.y);
 
         // P_t and O_t may only change once P_t(j-1) V has finished: it was issued when this warpgroup
-        // delivered P_t(j-1), a whole exponential section ago. (For j = 0 the previous item's epilogue
-        // has already waited for its last P V.)
-        if (j > 0) {
+        // delivered P_t(j-1), a whole exponential section ago. On the first tile of an item the P V in
+        // question is the last one of the previous item, and this is where that item's output is written:
+        // its epilogue hides behind this item's first exponentials instead of stalling the pipeline.
+        if (j == 0) {
+          if (pend) {
+            ok = finish_item();
+            if (!ok) break;
+          }
+        } else {
           ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done[t], (step - 1) & 1, abort_flag));
           if (!ok) break;
           tc_fence_after_sync();
@@ -630,30 +721,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       if (!ok) break;
 
-      // ---- epilogue of the item: O_t / l -> global ----------------------------------------------------
-      ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done[t], (g + kv_tiles - 1) & 1, abort_flag));
-      if (!ok) break;
-      tc_fence_after_sync();
-      float o[kHeadDim];
-      tmem_ld_x64(o_addr, reinterpret_cast<uint32_t*>(o));
-      tc_fence_before_sync();
-      warp_arrive(&sm.o_free[t], lane);  // the next item's first P V may overwrite O_t
-      if (row_valid) {
-        const float inv = 1.f / l_sum;
-        T* dst = reinterpret_cast<T*>(p.o) + b * p.o_sb + static_cast<int64_t>(q_row) * p.o_sn + h * p.o_sh;
-#pragma unroll
-        for (int ch = 0; ch < kHeadDim / 8; ++ch) {
-          uint4 val;
-          val.x = pack2<T>(o[ch * 8 + 0] * inv, o[ch * 8 + 1] * inv);
-          val.y = pack2<T>(o[ch * 8 + 2] * inv, o[ch * 8 + 3] * inv);
-          val.z = pack2<T>(o[ch * 8 + 4] * inv, o[ch * 8 + 5] * inv);
-          val.w = pack2<T>(o[ch * 8 + 6] * inv, o[ch * 8 + 7] * inv);
-          *reinterpret_cast<uint4*>(dst + ch * 8) = val;
-        }
-      }
+      // The item's output is written later (see above); remember what its epilogue needs.
+      pend = true;
+      pend_phase = (g + kv_tiles - 1) & 1;
+      pend_inv = 1.f / l_sum;
+      pend_dst = row_valid ? reinterpret_cast<T*>(p.o) + b * p.o_sb + static_cast<int64_t>(q_row) * p.o_sn + h * p.o_sh
+                           : nullptr;
       g += kv_tiles;
       if (w.n_tiles == 2) gp += kv_tiles;
     }
+    if (ok && pend) ok = finish_item();
     if (!ok && lane == 0) {
       if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusSoftmax);
     }

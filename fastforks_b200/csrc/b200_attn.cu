@@ -220,12 +220,20 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
   if (bias_mode == kBiasDense) {
     prm.bias = BiasView{a->bias, a->bias_stride[0], a->bias_stride[1], a->bias_stride[2],
                         static_cast<int>(a->bias_dtype)};
+    // Vector loads need every row segment that starts at a multiple of 128 columns to be 16-byte aligned.
+    prm.bias_vec = aligned16(a->bias) && a->bias_stride[0] % 8 == 0 && a->bias_stride[1] % 8 == 0 &&
+                   a->bias_stride[2] % 8 == 0;
   } else if (bias_mode == kBiasDecomposed) {
     prm.bias = BiasView{a->rel_h, a->rel_h_stride[0], a->rel_h_stride[1], a->rel_h_stride[2],
                         static_cast<int>(a->rel_dtype)};
     prm.bias2 = BiasView{a->rel_w, a->rel_w_stride[0], a->rel_w_stride[1], a->rel_w_stride[2],
                          static_cast<int>(a->rel_dtype)};
+    prm.rel_kh = a->rel_kh;
     prm.rel_kw = a->rel_kw;
+    prm.rel_staged = a->rel_kh + a->rel_kw <= kRelStageWords - 1;
+    if (a->rel_kw == 64 && a->rel_dtype != B200_ATTN_F32 && aligned16(a->rel_w) && a->rel_w_stride[0] % 8 == 0 &&
+        a->rel_w_stride[1] % 8 == 0 && a->rel_w_stride[2] % 8 == 0)
+      bias_mode = kBiasDecomposed64;
   }
   cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&prm.status), g_status_word);
   if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(status word)");
@@ -233,7 +241,6 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
 #ifdef B200_TRACE
   prm.trace = g_trace_buffer;
 #endif
-  if (const char* f = std::getenv("B200_ATTN_FLAGS")) prm.flags = std::atoi(f);
   const bool f16 = a->dtype == B200_ATTN_F16;
   switch (bias_mode) {
     case kBiasNone:
@@ -242,6 +249,9 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
     case kBiasDense:
       return f16 ? launch<__half, kBiasDense>(a, prm, mq, mk, mv, stream)
                  : launch<__nv_bfloat16, kBiasDense>(a, prm, mq, mk, mv, stream);
+    case kBiasDecomposed64:
+      return f16 ? launch<__half, kBiasDecomposed64>(a, prm, mq, mk, mv, stream)
+                 : launch<__nv_bfloat16, kBiasDecomposed64>(a, prm, mq, mk, mv, stream);
     default:
       return f16 ? launch<__half, kBiasDecomposed>(a, prm, mq, mk, mv, stream)
                  : launch<__nv_bfloat16, kBiasDecomposed>(a, prm, mq, mk, mv, stream);

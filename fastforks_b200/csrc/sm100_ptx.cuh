@@ -102,6 +102,28 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// The same for the helper threads (loader, MMA issuers): they sleep between polls so that their spinning does not
+// take issue slots from the softmax warps that share their SM sub-partition. Their wake-up latency is off the
+// critical path: loads run several tiles ahead and the MMAs are issued one to two tiles ahead of their use.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+  for (uint32_t polls = 0; polls < 4096; ++polls) {
+    __nanosleep(64);
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  const uint64_t t0 = global_timer_ns();
+  uint32_t polls = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(256);
+    if ((++polls & 0xff) == 0) {
+      if (*abort_flag != 0) return false;
+      if (global_timer_ns() - t0 > B200_WAIT_LIMIT_NS) return false;
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Proxy / tcgen05 fences
 // ---------------------------------------------------------------------------------------------
