@@ -48,6 +48,20 @@ REGIMES = (
     ("vit-b16 [1,12,197,64] fp16", 1, 12, 197, "fp16", None),
 )
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0}
+# Small single-kernel cases for profiler captures: `python bench.py --case NAME --launches L` launches the attention
+# kernel L times on one set of buffers and exits (name -> batch, heads, tokens, dtype, rel grid).
+CASES = {
+    "dinov2-vits14": (8, 6, 1370, "fp16", None),
+    "dav2-l": (4, 16, 1370, "bf16", None),
+    "sam-global": (1, 12, 4096, "fp16", (64, 64)),
+    "sam-windows": (25, 12, 196, "fp16", (14, 14)),
+    "vit-b16-b256": (256, 12, 197, "fp16", None),
+    "vit-b16-b1": (1, 12, 197, "fp16", None),
+}
+# DRAM bytes of one launch of the headline kernel ([8,6,1370,64] fp16), dram__bytes_read.sum + dram__bytes_write.sum
+# of the capture summarised in profiles/attn_fwd_dinov2-vits14.md: q, k, v are read once (25.3 MB), the 8.4 MB
+# output is still in L2 when the kernel ends.
+TRAFFIC_BYTES_PER_LAUNCH = 25.3e6
 
 
 def attention_flops(b: int, h: int, n: int, nk: int | None = None) -> float:
@@ -318,7 +332,8 @@ def run_ours(args: argparse.Namespace) -> None:  # noqa: PLR0915
             "peak": peaks["bf16_tflops"],
             "unit": "TFLOP/s",
             "frac": achieved / peaks["bf16_tflops"],
-            "traffic": None,
+            "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+            "algorithmic_bytes": attention_bytes(b, h, n),
             "peak_source": f"{peak_kind} (cuBLAS bf16 burst)",
             "kernel": "attn_fwd_kernel<half, no bias>",
             "us_per_launch": per_launch_ms * 1e3,
@@ -375,15 +390,40 @@ def run_ours(args: argparse.Namespace) -> None:  # noqa: PLR0915
         dist.destroy_process_group()
 
 
+def run_case(args: argparse.Namespace) -> None:
+    """Launch one named case `--launches` times without timing: the command profiler captures run."""
+    import torch
+
+    import fastforks_b200 as ff
+
+    b, h, n, dtype, rel = CASES[args.case]
+    dt = torch.float16 if dtype == "fp16" else torch.bfloat16
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    qkv = torch.randn(b, n, 3, h, HEAD_DIM, device="cuda", generator=gen).to(dt)
+    q, k, v = qkv.unbind(2)
+    out = torch.empty(b, n, h, HEAD_DIM, device="cuda", dtype=dt)
+    rels = None
+    if rel:
+        rels = tuple(torch.randn(b, h, n, r, device="cuda", generator=gen).to(dt) for r in rel)
+    for _ in range(args.launches):
+        ff.attention(q, k, v, layout="bnhd", out=out, rel=rels)
+    torch.cuda.synchronize()
+    print(json.dumps({"case": args.case, "launches": args.launches, "status": ff.device_status()}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--case", choices=tuple(CASES), default=None, help="launch one kernel case for a profiler and exit")
+    ap.add_argument("--launches", type=int, default=4)
     args = ap.parse_args()
     args.steps = max(1, args.steps)
-    if args.impl == "reference":
+    if args.case is not None:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
