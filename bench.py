@@ -219,6 +219,33 @@ def run_reference(args: argparse.Namespace) -> None:
     print(json.dumps(line))
 
 
+def model_throughput(torch, ff, dist, world: int, timed) -> dict | None:  # noqa: ANN001
+    """images/s of the kernels-mode ViT-L/14 encoder at 518 px, batch 4 per GPU (aggregate over ranks)."""
+    from fastforks_b200.vit import CONFIGS, ViTEncoder, seeded_state
+
+    cfg = CONFIGS["dinov2-vitl14"]
+    batch, side, steps = 4, 518, 5
+    enc = ViTEncoder(cfg, seeded_state(cfg, 0), device="cuda", dtype=torch.bfloat16)
+    images = torch.rand(batch, 3, side, side, generator=torch.Generator().manual_seed(1)).cuda()
+    out = None
+    for _ in range(3):
+        out = enc(images)
+
+    def forward() -> None:
+        enc(images)
+
+    ms = timed(forward, steps)
+    if ff.device_status() != 0 or not bool(torch.isfinite(out).all()):
+        return None
+    return {
+        "name": "dinov2-vitl14 (Depth-Anything-V2-L encoder) at 518 px, bf16",
+        "batch_per_gpu": batch,
+        "images_per_s": batch * steps * world / (ms * 1e-3),
+        "ms_per_forward": ms / steps,
+        "attention_gflop_per_image": enc.attention_flops(1, side, side) / 1e9,
+    }
+
+
 def time_launches(fn, reps: int, torch) -> float:  # noqa: ANN001
     """Average milliseconds of `fn()` over `reps` back-to-back calls, CUDA events on the current stream."""
     for _ in range(3):
@@ -347,6 +374,13 @@ def run_ours(args: argparse.Namespace) -> None:  # noqa: PLR0915
         gpu_launches=args.steps * layers,
         clocks=clocks.summary(),
     )
+
+    # Whole-model throughput of the caller of the hot path: the ViT-L/14 encoder of Depth-Anything-V2-L / DINOv2-L at
+    # 518 px (N = 1370, 24 layers, 16 heads), bf16, random-init weights, on every rank's own images. GEMMs, LayerNorm
+    # and GELU are torch library calls; the attention is this repository's kernel.
+    model = model_throughput(torch, ff, dist, world, timed)
+    if model is not None:
+        line["model"] = model
 
     if rank == 0:
         regimes = {}

@@ -34,7 +34,10 @@ NVCC_FLAGS = (
 )  # fmt: skip
 
 # Every symbol include/b200_attn.h declares.
-EXPORTS = ("b200_attn_fwd", "b200_attn_query", "b200_attn_status", "b200_attn_last_error", "b200_attn_version")
+EXPORTS = (
+    "b200_attn_fwd", "b200_attn_query", "b200_attn_status", "b200_attn_selftest_wait_limit", "b200_attn_last_error",
+    "b200_attn_version",
+)  # fmt: skip
 
 OK, UNSUPPORTED, BAD_CONFIG, CUDA_ERROR_BASE = 0, 1, -1, 1000
 F16, BF16, F32 = 0, 1, 2
@@ -134,6 +137,8 @@ def library() -> ctypes.CDLL:
     lib.b200_attn_query.restype = ctypes.c_int
     lib.b200_attn_status.argtypes = (ctypes.POINTER(ctypes.c_uint32),)
     lib.b200_attn_status.restype = ctypes.c_int
+    lib.b200_attn_selftest_wait_limit.argtypes = (ctypes.c_uint32, ctypes.c_void_p)
+    lib.b200_attn_selftest_wait_limit.restype = ctypes.c_int
     lib.b200_attn_last_error.argtypes = ()
     lib.b200_attn_last_error.restype = ctypes.c_char_p
     lib.b200_attn_version.argtypes = ()

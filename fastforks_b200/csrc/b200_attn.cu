@@ -21,6 +21,21 @@ using namespace b200;
 // Role bits of waits that gave up; one word per device that loaded the library.
 __device__ uint32_t g_status_word;
 
+// A wait that can never be satisfied, with a caller-chosen limit: exercises the path every kernel wait takes when
+// it gives up (error bit in the status word, normal return) without faulting, trapping or hanging anything.
+__global__ void wait_limit_selftest_kernel(uint64_t limit_ns, uint32_t* status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);  // nobody ever arrives
+    mbar_init_fence();
+  }
+  __syncthreads();
+  const uint64_t t0 = global_timer_ns();
+  bool done = false;
+  while (!done && global_timer_ns() - t0 <= limit_ns) done = mbar_try_wait(&bar, 0);
+  if (!done && threadIdx.x == 0) atomicOr(status, 8u);
+}
+
 thread_local char tl_error[512] = "";
 
 #ifdef B200_TRACE
@@ -276,6 +291,18 @@ int b200_attn_status(uint32_t* status) {
 #ifdef B200_TRACE
 void b200_attn_debug_set_trace(void* device_buffer) { g_trace_buffer = static_cast<long long*>(device_buffer); }
 #endif
+
+int b200_attn_selftest_wait_limit(uint32_t limit_us, void* stream_ptr) {
+  if (limit_us == 0 || limit_us > 100000)
+    return fail(B200_ATTN_BAD_CONFIG, "limit_us %u must be between 1 and 100000", limit_us);
+  uint32_t* status = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_status_word);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(status word)");
+  wait_limit_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_ptr)>>>(uint64_t(limit_us) * 1000, status);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "self-test kernel launch");
+  return B200_ATTN_OK;
+}
 
 const char* b200_attn_last_error(void) { return tl_error; }
 

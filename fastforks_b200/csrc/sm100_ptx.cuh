@@ -54,17 +54,6 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t done;
-#ifdef B200_TEST_WAIT
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-#else
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
@@ -74,7 +63,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(done)
       : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
-#endif
+  return done != 0;
+}
+
+// Non-blocking probe: true when the phase with the given parity has completed.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
   return done != 0;
 }
 
@@ -297,6 +300,29 @@ __device__ __forceinline__ void tmem_ld_x64(uint32_t taddr, uint32_t* v) {
       : B200_R16(v, 0), B200_R16(v, 16), B200_R16(v, 32), B200_R16(v, 48)
       : "r"(taddr), "r"(taddr + 32)
       : "memory");
+}
+
+// Asynchronous load: the registers are valid only after tmem_ld_wait_pin() on the same registers.
+__device__ __forceinline__ void tmem_ld_x32_nowait(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : B200_R16(v, 0), B200_R16(v, 16)
+      : "r"(taddr)
+      : "memory");
+}
+
+#define B200_P4(v, i) "+r"(v[i]), "+r"(v[i + 1]), "+r"(v[i + 2]), "+r"(v[i + 3])
+#define B200_P16(v, i) B200_P4(v, i), B200_P4(v, i + 4), B200_P4(v, i + 8), B200_P4(v, i + 12)
+
+// Waits for all of this thread's tensor-memory loads. The 32 registers are routed through the instruction so that
+// no use of them is scheduled before the wait; call tmem_ld_pin() for further registers of the same batch.
+__device__ __forceinline__ void tmem_ld_wait_pin(uint32_t* v) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" : B200_P16(v, 0), B200_P16(v, 16) : : "memory");
+}
+__device__ __forceinline__ void tmem_ld_pin(uint32_t* v) {
+  asm volatile("" : B200_P16(v, 0), B200_P16(v, 16) : : "memory");
 }
 
 __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t* v) {

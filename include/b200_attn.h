@@ -41,10 +41,12 @@ extern "C" {
 #define B200_ATTN_BF16 1
 #define B200_ATTN_F32 2 /* bias tensors only */
 
-/* Tile schedules. AUTO picks by sequence length. */
+/* Tile schedule hints. One persistent schedule serves every sequence length today (one CTA per SM walks work items
+ * of one or two 128-row query tiles of one head, the next item's tiles prefetched while the current one computes),
+ * so the three values run the same kernel; they are part of the ABI so that a caller's hint keeps its meaning. */
 #define B200_ATTN_SCHED_AUTO 0
-#define B200_ATTN_SCHED_LONG 1  /* one or two 128-row query tiles of one head per CTA, K/V streamed */
-#define B200_ATTN_SCHED_SHORT 2 /* persistent CTAs walking many (batch, head) pairs, next head prefetched */
+#define B200_ATTN_SCHED_LONG 1
+#define B200_ATTN_SCHED_SHORT 2
 
 /*
  * One attention call.  Element (b, n, h, d) of q lives at q + b*q_stride[0] + n*q_stride[1] + h*q_stride[2] + d
@@ -118,6 +120,15 @@ int b200_attn_query(const B200AttnArgs* args, int32_t* schedule);
  * The reference has no counterpart: its kernels contain no waits on asynchronous units.
  */
 int b200_attn_status(uint32_t* status);
+
+/*
+ * Launches a one-warp kernel that waits, for at most `limit_us` microseconds (1..100000), on a barrier that nothing
+ * ever completes, then gives up the way every wait in the attention kernels does: it sets bit 8 of the device
+ * status word and returns normally.  `b200_attn_status` must then report 8, and the context stays usable.
+ * It exists so that the give-up path can be tested without faulting, trapping or hanging a GPU.
+ * The reference has no counterpart.
+ */
+int b200_attn_selftest_wait_limit(uint32_t limit_us, void* stream);
 
 /* Human-readable reason of the calling thread's last non-zero return. Never NULL. */
 const char* b200_attn_last_error(void);

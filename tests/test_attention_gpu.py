@@ -267,3 +267,21 @@ def test_contract_violations_raise_before_launch() -> None:
         ff.attention(q.clone().requires_grad_(), q, q, layout="bnhd")
     with pytest.raises(ValueError, match="exclusive"):
         ff.attention(q, q, q, layout="bnhd", bias=torch.zeros(5, 5, device="cuda"), rel=(q, q))
+
+
+def test_a_wait_that_runs_out_sets_the_status_word_and_the_context_survives() -> None:
+    """Every wait in the kernels is bounded. The self-test kernel waits 2 ms on a barrier nothing completes, gives up
+    like the attention kernels do, and the next attention call still runs and is correct."""
+    import ctypes
+
+    from fastforks_b200 import _lib
+
+    assert ff.device_status() == 0
+    stream = torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())  # noqa: SLF001
+    assert _lib.library().b200_attn_selftest_wait_limit(2000, ctypes.c_void_p(stream)) == 0
+    assert ff.device_status() == 8  # read and cleared
+    assert ff.device_status() == 0
+    qkv = packed_qkv(1, 130, 2, torch.float16, 1.0, 3)
+    q, k, v = qkv.unbind(2)
+    got = ff.attention(q, k, v, layout="bnhd")
+    assert_close(got.float().cpu().numpy(), oracle_of_packed(qkv, 0.125), unit_scale=True)
