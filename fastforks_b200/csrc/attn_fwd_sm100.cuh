@@ -5,9 +5,9 @@
 // the keys of each in tiles of 128:
 //   * a loader warp stages Q once and K / V tiles through rings of shared-memory stages with TMA
 //     (128-byte swizzle, rows past the end of the sequence read as zero); K runs two tiles ahead of V;
-//   * an MMA warp issues S = Q K^T (tcgen05.mma, M=128 N=128 K=64) into tensor memory and
-//     O += P V (M=128 N=64 K=128) with P read straight from tensor memory. S_t(j+2) is issued as soon
-//     as the softmax threads have pulled S_t(j+1) into registers, so the tensor pipe never sits on the
+//   * one thread per query tile issues S = Q K^T (tcgen05.mma, M=128 N=128 K=64) into tensor memory and
+//     O += P V (M=128 N=64 K=128) with P read straight from tensor memory. S_t(j+1) is issued as soon
+//     as the softmax threads have pulled S_t(j) into registers, so the tensor pipe never sits on the
 //     softmax critical path;
 //   * two softmax warpgroups, one per query tile, own one row of S per thread: they read the row
 //     from tensor memory, keep the running maximum and sum, and write P back as 16-bit values.
@@ -34,7 +34,7 @@ constexpr int kTileRows = 128;                        // query rows per tile == 
 constexpr int kHeadDim = 64;                          // the only head dim of this path
 constexpr int kTileBytes = kTileRows * kHeadDim * 2;  // one Q / K / V tile in shared memory
 constexpr int kLoaderWarp = 8;
-constexpr int kMmaWarp = 9;                             // warps 9 and 10 issue the MMAs of query tile 0 and 1
+constexpr int kMmaWarp = 9;                           // warps 9 and 10 issue the MMAs of query tile 0 and 1
 constexpr int kThreads = 384;                         // 2 softmax warpgroups + 1 warpgroup of helpers (1 idle warp)
 constexpr int kSoftmaxRegs = 224, kHelperRegs = 56;   // per-thread register budgets after the hand-over
 constexpr int kLaunchRegs = 168;                      // what a 384-thread CTA gets per thread at launch
@@ -54,13 +54,14 @@ enum : uint32_t { kStatusLoader = 1, kStatusMma = 2, kStatusSoftmax = 4 };
 // Development aid, compiled out of the shipped library: with -DB200_TRACE one lane per role of CTA 0 writes
 // clock stamps to AttnParams::trace so that the pipeline's timeline can be read back.
 #ifdef B200_TRACE
-#define B200_STAMP(role, iter, slot)                                                                    \
-  do {                                                                                                  \
-    if (blockIdx.x == 0 && lane == 0 && p.trace != nullptr && (iter) < 32) {                            \
-      long long t_;                                                                                     \
-      asm volatile("mov.u64 %0, %%clock64;" : "=l"(t_));                                                \
-      p.trace[((role) * 32 + (iter)) * 8 + (slot)] = t_;                                                \
-    }                                                                                                   \
+// Stamps go to shared memory (one store, no divergent global access) and are copied out when the CTA leaves.
+#define B200_STAMP(role, iter, slot)                                               \
+  do {                                                                             \
+    if (lane == 0 && (iter) < 32) {                                                \
+      uint32_t t_;                                                                 \
+      asm volatile("mov.u32 %0, %%clock;" : "=r"(t_));                             \
+      sm.trace[((role) * 32 + (iter)) * 8 + (slot)] = t_;                          \
+    }                                                                              \
   } while (0)
 #else
 #define B200_STAMP(role, iter, slot) \
@@ -89,6 +90,7 @@ struct AttnParams {
   BiasView bias;       // dense bias, or rel_h of the decomposed form
   BiasView bias2;      // rel_w of the decomposed form
   int rel_kh, rel_kw;
+  uint64_t magic_pairs, magic_heads, magic_rel_kw;  // fast_div constants of q_tiles / 2, heads, rel_kw
   int rel_staged;      // decomposed form: rel_kh + rel_kw <= 32, rows are staged in shared memory per item
   int bias_vec;        // dense form: rows are 16-byte aligned, full tiles are read with vector loads
   uint32_t* status;    // device word that collects role bits of expired waits
@@ -111,6 +113,9 @@ struct alignas(1024) AttnSmem {
   uint64_t turn[2];     // the other warpgroup is half way through its exponentials: t may start (4 warps)
   uint32_t tmem_base;
   uint32_t abort;
+#ifdef B200_TRACE
+  uint32_t trace[12 * 32 * 8];
+#endif
   float rel_stage[2][kTileRows][kRelStageWords];  // each softmax thread's own rel_h | rel_w row, times log2(e)
 };
 
@@ -202,6 +207,13 @@ __device__ __forceinline__ float load_bias_elem(const void* base, int dtype, int
   return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(base) + idx));
 }
 
+// n / d for the divisors the host knows at launch: magic = ceil(2^64 / d) (0 stands for d == 1), exact for every
+// n * d < 2^64. An integer division in device code takes its reciprocal from the MUFU unit, which the softmax warps
+// keep saturated; the multiply does not.
+__device__ __forceinline__ int fast_div(int n, uint64_t magic) {
+  return magic == 0 ? n : static_cast<int>(__umul64hi(static_cast<uint64_t>(static_cast<uint32_t>(n)), magic));
+}
+
 // One unit of work: one or two 128-row query tiles of one (batch, head).
 struct WorkItem {
   int b, h, q_row0, n_tiles;
@@ -217,7 +229,7 @@ __device__ __forceinline__ WorkItem decode_item(const AttnParams& p, int item_id
   const int doubles = pairs * p.batch * p.heads;
   int bh;
   if (item_id < doubles) {
-    bh = item_id / pairs;
+    bh = fast_div(item_id, p.magic_pairs);
     w.q_row0 = (item_id - bh * pairs) * 2 * kTileRows;
     w.n_tiles = 2;
   } else {
@@ -225,8 +237,8 @@ __device__ __forceinline__ WorkItem decode_item(const AttnParams& p, int item_id
     w.q_row0 = pairs * 2 * kTileRows;
     w.n_tiles = 1;
   }
-  w.b = bh / p.heads;
-  w.h = bh % p.heads;
+  w.b = fast_div(bh, p.magic_heads);
+  w.h = bh - w.b * p.heads;
   return w;
 }
 
@@ -274,6 +286,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&sm.v_empty[i], 2);
     }
     sm.abort = 0;
+#ifdef B200_TRACE
+    for (int i = 0; i < 12 * 32 * 8; ++i) sm.trace[i] = 0;
+#endif
     mbar_init_fence();
   }
   if (warp == kMmaWarp) {
@@ -356,8 +371,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const uint32_t idesc_qk_last = umma_idesc_f16(fmt, kTileRows, kv_last16, 0, 0);
         bool ok = true;
 
-        // Everything the issue loops need is computed once: one thread feeds the tensor pipe, and every
-        // instruction between two tcgen05.mma shows up as an idle pipe when the MMAs are this small.
+        // Everything the issue loops need is computed once or counted along: one thread feeds the tensor pipe, and
+        // every instruction between two tcgen05.mma shows up as an idle pipe when the MMAs are this small.
         const uint64_t q_desc0 = umma_smem_desc_sw128(smem_u32(sm.q[t][0]), 1024, 16);
         const uint64_t k_desc0 = umma_smem_desc_sw128(smem_u32(sm.k[0]), 1024, 16);
         const uint64_t v_desc0 = umma_smem_desc_sw128(smem_u32(sm.v[0]), 1024, 0);
@@ -371,67 +386,95 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint64_t* const pv_done = &sm.pv_done[t];
 
         // This slot's items are a prefix of the CTA's list (two-tile items come first), so its key-tile steps form
-        // one stream gs = 0, 1, ...: step gs is tile gs % kv_tiles of item gs / kv_tiles and uses ring tile gs.
-        // S is issued two steps ahead of its use, across item boundaries too, so that a new item starts at once.
+        // one stream gs = 0, 1, ...: step gs is key tile j of item it and uses ring tile gs (stage st, in its
+        // ph-th use). S is issued two steps ahead of its use, across item boundaries too, so that a new item starts
+        // at once. The positions are counted along: a division by kv_tiles here would queue its reciprocal behind the
+        // softmax warps' exponentials on the MUFU unit, which cost the long-sequence runs 15 %.
         const int total_doubles = (p.q_tiles >> 1) * p.batch * p.heads;
         int my_doubles = (total_doubles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
                          static_cast<int>(gridDim.x);
         my_doubles = my_doubles < 0 ? 0 : (my_doubles > my_items ? my_items : my_doubles);
         const int total_steps = (t == 0 ? my_items : my_doubles) * kv_tiles;
+        struct Pos {
+          int gs, it, j, st;
+          uint32_t ph;
+        };
+        auto advance = [&](Pos& x) {
+          ++x.gs;
+          if (++x.j == kv_tiles) {
+            x.j = 0;
+            ++x.it;
+          }
+          if (++x.st == kStagesK) {
+            x.st = 0;
+            x.ph ^= 1;
+          }
+        };
+        static_assert(kStagesK == kStagesV, "one ring position serves both rings");
 
         // S_t(gs) = Q_t K^T. The last key tile of an item only computes the columns that hold keys.
-        auto issue_qk = [&](int gs) -> bool {
-          const int it = gs / kv_tiles, j = gs - it * kv_tiles, slot = it & 1, st = gs % kStagesK;
-          if (!mbar_wait_relaxed(&sm.k_full[st], (gs / kStagesK) & 1, abort_flag)) return false;
-          if (j == 0 && !mbar_wait_relaxed(&sm.q_full[t][slot], (it >> 1) & 1, abort_flag)) return false;
-          if (gs > 0 && !mbar_wait_relaxed(s_free, (gs - 1) & 1, abort_flag)) return false;  // S_t has been read
+        auto issue_qk = [&](const Pos& x) -> bool {
+          const int slot = x.it & 1;
+          // The K tile landed long ago as a rule: its test is issued first and runs behind the wait that does wait.
+          const bool k_early = mbar_test_wait(&sm.k_full[x.st], x.ph);
+          if (x.j == 0 && !mbar_wait(&sm.q_full[t][slot], (x.it >> 1) & 1, abort_flag)) return false;
+          if (x.gs > 0 && !mbar_wait(s_free, (x.gs - 1) & 1, abort_flag)) return false;  // S_t has been read
+          if (!k_early && !mbar_wait(&sm.k_full[x.st], x.ph, abort_flag)) return false;
           tc_fence_after_sync();
+          B200_STAMP(2 + t, x.gs, 2);
           const uint64_t a = q_desc0 + static_cast<uint64_t>(slot) * kStageStep;
-          const uint64_t bd = k_desc0 + static_cast<uint64_t>(st) * kStageStep;
-          const uint32_t idesc = (j == kv_tiles - 1) ? idesc_qk_last : idesc_qk;
+          const uint64_t bd = k_desc0 + static_cast<uint64_t>(x.st) * kStageStep;
+          const uint32_t idesc = (x.j == kv_tiles - 1) ? idesc_qk_last : idesc_qk;
 #pragma unroll
           for (int kk = 0; kk < kHeadDim / 16; ++kk)  // 32 bytes of K per step inside the swizzle atom
             umma_ss(s_tm, a + 2 * kk, bd + 2 * kk, idesc, kk > 0 ? 1u : 0u);
           umma_commit(s_full);
-          umma_commit(&sm.k_empty[st]);
-          if (it >= my_doubles) umma_commit(&sm.k_empty[st]);  // one-tile item: stand in for the absent second tile
-          if (j == kv_tiles - 1) umma_commit(&sm.q_empty[t][slot]);  // the item's last reader of Q_t
+          umma_commit(&sm.k_empty[x.st]);
+          if (x.it >= my_doubles) umma_commit(&sm.k_empty[x.st]);  // one-tile item: stand in for the absent second tile
+          if (x.j == kv_tiles - 1) umma_commit(&sm.q_empty[t][slot]);  // the item's last reader of Q_t
+          B200_STAMP(2 + t, x.gs, 3);
           return true;
         };
         // O_t (+)= P_t(gs) V, 16 keys (two 8-row groups of the V tile) per MMA.
-        auto issue_pv = [&](int gs) -> bool {
-          const int it = gs / kv_tiles, j = gs - it * kv_tiles, st = gs % kStagesV;
-          if (!mbar_wait_relaxed(&sm.v_full[st], (gs / kStagesV) & 1, abort_flag)) return false;
-          if (!mbar_wait_relaxed(p_full, gs & 1, abort_flag)) return false;
+        auto issue_pv = [&](const Pos& x) -> bool {
+          const bool v_early = mbar_test_wait(&sm.v_full[x.st], x.ph);
+          if (!mbar_wait(p_full, x.gs & 1, abort_flag)) return false;
+          if (!v_early && !mbar_wait(&sm.v_full[x.st], x.ph, abort_flag)) return false;
           // The first P V of an item overwrites O_t: the previous item's epilogue must have read it.
-          if (j == 0 && it > 0 && !mbar_wait_relaxed(&sm.o_free[t], (it - 1) & 1, abort_flag)) return false;
+          if (x.j == 0 && x.it > 0 && !mbar_wait(&sm.o_free[t], (x.it - 1) & 1, abort_flag)) return false;
           tc_fence_after_sync();
-          B200_STAMP(2 + t, gs, 0);
-          const uint64_t bd = v_desc0 + static_cast<uint64_t>(st) * kStageStep;
-          if (j != kv_tiles - 1) {
-            umma_ts(o_tm, p_tm, bd, idesc_pv, j > 0 ? 1u : 0u);
+          B200_STAMP(2 + t, x.gs, 0);
+          const uint64_t bd = v_desc0 + static_cast<uint64_t>(x.st) * kStageStep;
+          if (x.j != kv_tiles - 1) {
+            umma_ts(o_tm, p_tm, bd, idesc_pv, x.j > 0 ? 1u : 0u);
 #pragma unroll
             for (int kk = 1; kk < kTileRows / 16; ++kk)
               umma_ts(o_tm, p_tm + kk * 8, bd + kk * (2048 >> 4), idesc_pv, 1u);
           } else {
             const int steps = kv_last16 / 16;  // at least one
-            umma_ts(o_tm, p_tm, bd, idesc_pv, j > 0 ? 1u : 0u);
+            umma_ts(o_tm, p_tm, bd, idesc_pv, x.j > 0 ? 1u : 0u);
 #pragma unroll
             for (int kk = 1; kk < kTileRows / 16; ++kk)
               if (kk < steps) umma_ts(o_tm, p_tm + kk * 8, bd + kk * (2048 >> 4), idesc_pv, 1u);
           }
           umma_commit(pv_done);
-          umma_commit(&sm.v_empty[st]);
-          if (it >= my_doubles) umma_commit(&sm.v_empty[st]);
-          B200_STAMP(2 + t, gs, 1);
+          umma_commit(&sm.v_empty[x.st]);
+          if (x.it >= my_doubles) umma_commit(&sm.v_empty[x.st]);
+          B200_STAMP(2 + t, x.gs, 1);
           return true;
         };
 
-        if (total_steps > 0) ok = issue_qk(0);
-        if (ok && total_steps > 1) ok = issue_qk(1);
-        for (int gs = 0; gs < total_steps && ok; ++gs) {
-          ok = issue_pv(gs);
-          if (ok && gs + 2 < total_steps) ok = issue_qk(gs + 2);
+        Pos xq = {0, 0, 0, 0, 0u};  // the Q K^T stream runs two steps ahead of the P V stream
+        for (int i = 0; i < 2 && xq.gs < total_steps && ok; ++i) {
+          ok = issue_qk(xq);
+          advance(xq);
+        }
+        for (Pos xp = {0, 0, 0, 0, 0u}; xp.gs < total_steps && ok; advance(xp)) {
+          ok = issue_pv(xp);
+          if (ok && xq.gs < total_steps) {
+            ok = issue_qk(xq);
+            advance(xq);
+          }
         }
         if (!ok) {
           if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusMma);
@@ -452,6 +495,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     int g = 0;        // key-tile steps of this slot so far (phases of s_full, s_free, p_full, pv_done)
     int gp = 0;       // steps so far in items where both warpgroups work (phases of the turn barriers)
     bool ok = true;
+    bool bad = false;  // this lane gave up a wait since the last vote
+    bool s_early = false, pv_early = false;  // early barrier tests (see the step loop)
     // Epilogue of the previous item, still to be done: its last P V phase, 1 / row sum, output row (or null).
     bool pend = false;
     uint32_t pend_phase = 0;
@@ -516,21 +561,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
       for (int j = 0; j < kv_tiles; ++j) {
         const int step = g + j;
-        ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_full[t], step & 1, abort_flag));
-        if (!ok) break;
+        // One vote per step on whether any lane's wait ran out during the previous one.
+        if (__any_sync(0xffffffffu, bad)) {
+          ok = false;
+          break;
+        }
+        bad |= !mbar_wait_warp_after(s_early, &sm.s_full[t], step & 1, abort_flag);
         tc_fence_after_sync();
         if ((warp & 3) == 0) B200_STAMP(t, step, 0);
 
         float s[kTileRows];
         {
           uint32_t* su = reinterpret_cast<uint32_t*>(s);
-          tmem_ld_x64(s_addr, su);
-          tmem_ld_x64(s_addr + 64, su + 64);
+          // Four loads in flight, one wait.
+#pragma unroll
+          for (int q = 0; q < 4; ++q) tmem_ld_x32_nowait(s_addr + 32 * q, su + 32 * q);
+          tmem_ld_wait_pin(su);
+#pragma unroll
+          for (int q = 1; q < 4; ++q) tmem_ld_pin(su + 32 * q);
         }
         // S_t is in registers: the tensor pipe may overwrite it with the tile after next.
         tc_fence_before_sync();
         warp_arrive(&sm.s_free[t], lane);
         if ((warp & 3) == 0) B200_STAMP(t, step, 1);
+        // Tests of the barriers this step will wait on, issued here so that their latency (100-150 clocks each with
+        // tensor memory allocated) runs behind the arithmetic; a test that finds its phase pending is repeated as a
+        // real wait where the result is needed.
+        const bool need_turn = pingpong && (t == 1 || gp + j > 0);
+        const uint32_t turn_parity = (t == 0) ? ((gp + j - 1) & 1) : ((gp + j) & 1);
+        const bool turn_early = need_turn ? mbar_test_wait(&sm.turn[t], turn_parity) : true;
 
         const int kv0 = j * kTileRows;
         const int kv_valid = min(kTileRows, p.kv_tokens - kv0);
@@ -591,7 +650,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
           }
         } else if constexpr (BIAS == kBiasDecomposed) {
-          int ih = kv0 / p.rel_kw;
+          int ih = fast_div(kv0, p.magic_rel_kw);
           int iw = kv0 - ih * p.rel_kw;
           if (p.rel_staged) {
             const float* rh = sm.rel_stage[t][row_in_tile];
@@ -658,11 +717,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // may only start a section once the other is half way through its previous one: warpgroup 0 starts
         // step q+1 after warpgroup 1's midpoint of step q, warpgroup 1 starts step q after warpgroup 0's
         // midpoint of step q. Half a section apart, neither ever waits here.
-        if (pingpong && (t == 1 || gp + j > 0)) {
-          const uint32_t parity = (t == 0) ? ((gp + j - 1) & 1) : ((gp + j) & 1);
-          ok = __all_sync(0xffffffffu, mbar_wait(&sm.turn[t], parity, abort_flag));
-          if (!ok) break;
-        }
+        if (need_turn) bad |= !mbar_wait_warp_after(turn_early, &sm.turn[t], turn_parity, abort_flag);
         if ((warp & 3) == 0) B200_STAMP(t, step, 2);
         float2 l2a = make_float2(0.f, 0.f), l2b = make_float2(0.f, 0.f);
         const float2 c2 = (BIAS == kBiasNone) ? make_float2(c, c) : make_float2(1.f, 1.f);
@@ -684,6 +739,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
           // Midpoint: let the other warpgroup start. The second half reads `nm` through the arrival.
           if (half == 0 && pingpong) warp_arrive_pinned(&sm.turn[t ^ 1], lane, nm);
+          if (half == 0) {
+            pv_early = (j > 0) ? mbar_test_wait(&sm.pv_done[t], (step - 1) & 1) : true;
+            s_early = mbar_test_wait(&sm.s_full[t], (step + 1) & 1);  // the next step's S (unused after the last step)
+          }
         }
         if ((warp & 3) == 0) B200_STAMP(t, step, 3);
         l_sum += (l2a.x + l2a.y) + (l2b.x + l2b.y);
@@ -698,8 +757,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (!ok) break;
           }
         } else {
-          ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done[t], (step - 1) & 1, abort_flag));
-          if (!ok) break;
+          bad |= !mbar_wait_warp_after(pv_early, &sm.pv_done[t], (step - 1) & 1, abort_flag);
           tc_fence_after_sync();
           if (__any_sync(0xffffffffu, raise)) {
             float o[kHeadDim];
@@ -720,6 +778,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if ((warp & 3) == 0) B200_STAMP(t, step, 5);
       }
       if (!ok) break;
+      if (__any_sync(0xffffffffu, bad)) {
+        ok = false;
+        break;
+      }
 
       // The item's output is written later (see above); remember what its epilogue needs.
       pend = true;
@@ -739,6 +801,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // ---- common exit ----------------------------------------------------------------------------
   tc_fence_before_sync();
   __syncthreads();
+#ifdef B200_TRACE
+  if (blockIdx.x == 0 && p.trace != nullptr)
+    for (int i = threadIdx.x; i < 12 * 32 * 8; i += kThreads) p.trace[i] = sm.trace[i];
+#endif
   if (warp == kMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);

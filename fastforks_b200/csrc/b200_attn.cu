@@ -36,6 +36,9 @@ __global__ void wait_limit_selftest_kernel(uint64_t limit_ns, uint32_t* status) 
   if (!done && threadIdx.x == 0) atomicOr(status, 8u);
 }
 
+// ceil(2^64 / d) for the kernel's fast_div; 0 stands for d <= 1.
+uint64_t div_magic(int d) { return d <= 1 ? 0 : ~uint64_t(0) / static_cast<uint64_t>(d) + 1; }
+
 thread_local char tl_error[512] = "";
 
 #ifdef B200_TRACE
@@ -228,6 +231,8 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
   prm.items_per_head = (prm.q_tiles + 1) / 2;
   prm.kv_tiles = (a->kv_tokens + kTileRows - 1) / kTileRows;
   prm.scale_log2 = a->scale * kLog2e;
+  prm.magic_pairs = div_magic(prm.q_tiles / 2);
+  prm.magic_heads = div_magic(a->heads);
   prm.o = a->o;
   prm.o_sb = a->o_stride[0];
   prm.o_sn = a->o_stride[1];
@@ -245,6 +250,7 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
                          static_cast<int>(a->rel_dtype)};
     prm.rel_kh = a->rel_kh;
     prm.rel_kw = a->rel_kw;
+    prm.magic_rel_kw = div_magic(a->rel_kw);
     prm.rel_staged = a->rel_kh + a->rel_kw <= kRelStageWords - 1;
     if (a->rel_kw == 64 && a->rel_dtype != B200_ATTN_F32 && aligned16(a->rel_w) && a->rel_w_stride[0] % 8 == 0 &&
         a->rel_w_stride[1] % 8 == 0 && a->rel_w_stride[2] % 8 == 0)

@@ -105,9 +105,28 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
-// The same for the helper threads (loader, MMA issuers): they sleep between polls so that their spinning does not
-// take issue slots from the softmax warps that share their SM sub-partition. Their wake-up latency is off the
-// critical path: loads run several tiles ahead and the MMAs are issued one to two tiles ahead of their use.
+// Wait of a whole warp on a barrier whose phase has, as a rule, completed long ago: one poll and no vote on that
+// path. Returns false for a lane whose wait ran out; the caller collects that per lane and votes once per step.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  bool done = mbar_try_wait(bar, parity);
+  if (!done) done = mbar_wait(bar, parity, abort_flag);
+  __syncwarp();
+  return done;
+}
+
+// Second half of a wait whose first test was issued early (mbar_test_wait, its latency hidden behind other work):
+// `early` is that test's result; only a lane that saw the phase still pending waits now.
+__device__ __forceinline__ bool mbar_wait_warp_after(bool early, uint64_t* bar, uint32_t parity,
+                                                      volatile uint32_t* abort_flag) {
+  bool done = early;
+  if (!done) done = mbar_wait(bar, parity, abort_flag);
+  __syncwarp();
+  return done;
+}
+
+// The same for the loader thread: it sleeps between polls so that its spinning does not take issue slots from the
+// softmax warps that share its SM sub-partition. The sleep costs some 300 clocks of wake-up latency (80 without),
+// which is off the critical path here: loads run several tiles ahead. The MMA issuers use mbar_wait.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
 #pragma unroll 1
