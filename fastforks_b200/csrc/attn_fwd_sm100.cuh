@@ -68,9 +68,11 @@ enum : uint32_t { kStatusLoader = 1, kStatusMma = 2, kStatusSoftmax = 4 };
   do {                               \
   } while (0)
 #endif
-// Bias forms. kBiasDecomposed64 is the decomposed form specialised for rel_kw == 64 with 16-bit, 16-byte aligned
+// Bias forms. kBiasDecomposed14 is the decomposed form specialised for a 14 x 14 key grid (SAM's windows): both
+// tables of a row sit in registers and every column's pair of indices is a compile-time constant.
+// kBiasDecomposed64 is the decomposed form specialised for rel_kw == 64 with 16-bit, 16-byte aligned
 // rel_w rows (SAM's global layers): a key tile then spans exactly two rel_h entries and the whole rel_w row twice.
-enum : int { kBiasNone = 0, kBiasDense = 1, kBiasDecomposed = 2, kBiasDecomposed64 = 3 };
+enum : int { kBiasNone = 0, kBiasDense = 1, kBiasDecomposed = 2, kBiasDecomposed64 = 3, kBiasDecomposed14 = 4 };
 constexpr int kRelStageWords = 33;  // per-row staging of rel_h | rel_w in shared memory: up to 32 values, odd stride
 
 struct BiasView {
@@ -212,6 +214,28 @@ __device__ __forceinline__ float load_bias_elem(const void* base, int dtype, int
 // keep saturated; the multiply does not.
 __device__ __forceinline__ int fast_div(int n, uint64_t magic) {
   return magic == 0 ? n : static_cast<int>(__umul64hi(static_cast<uint64_t>(static_cast<uint32_t>(n)), magic));
+}
+
+// s[i] = s[i] * c + rel_h[(KV0 + i) / 14] + rel_w[(KV0 + i) % 14] for the keys of a 14 x 14 grid that fall into this
+// tile; `stage` (shared memory) holds the row's 14 rel_h and 14 rel_w values, already times log2(e). All indices are
+// constants: rel_w sits in registers for the section, each rel_h value is read once.
+template <int KV0>
+__device__ __forceinline__ void add_rel14(float* s, const float* stage, float c) {
+  float rw[14];
+#pragma unroll
+  for (int m = 0; m < 14; ++m) rw[m] = stage[14 + m];
+  const float2 cc = make_float2(c, c);
+#pragma unroll
+  for (int i = 0; i < kTileRows; i += 2) {
+    constexpr int kKeys = 14 * 14;  // even, so a pair of columns is inside or outside together
+    const int col = KV0 + i;
+    if (col < kKeys) {
+      const float2 b2 = fadd2(make_float2(stage[col / 14], stage[(col + 1) / 14]), make_float2(rw[col % 14], rw[(col + 1) % 14]));
+      const float2 r = ffma2(make_float2(s[i], s[i + 1]), cc, b2);
+      s[i] = r.x;
+      s[i + 1] = r.y;
+    }
+  }
 }
 
 // One unit of work: one or two 128-row query tiles of one (batch, head).
@@ -536,11 +560,43 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       float l_sum = 0.f;
 
       int64_t bias_row = 0, bias2_row = 0;
+      float rh_next0 = 0.f, rh_next1 = 0.f;             // kBiasDecomposed64: the coming step's two rel_h values
       if constexpr (BIAS != kBiasNone) {
         const int qr = row_valid ? q_row : 0;
         bias_row = b * p.bias.sb + h * p.bias.sh + qr * p.bias.sn;
-        if constexpr (BIAS == kBiasDecomposed || BIAS == kBiasDecomposed64)
+        if constexpr (BIAS == kBiasDecomposed || BIAS == kBiasDecomposed64 || BIAS == kBiasDecomposed14)
           bias2_row = b * p.bias2.sb + h * p.bias2.sh + qr * p.bias2.sn;
+        if constexpr (BIAS == kBiasDecomposed14) {
+          // This thread's rows, read back by this thread only: no synchronisation needed.
+          float* stage = sm.rel_stage[t][row_in_tile];
+          float tmp[28];
+#pragma unroll
+          for (int i = 0; i < 14; ++i) {  // all loads in flight together
+            tmp[i] = load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + i);
+            tmp[14 + i] = load_bias_elem(p.bias2.ptr, p.bias2.dtype, bias2_row + i);
+          }
+#pragma unroll
+          for (int i = 0; i < 28; ++i) stage[i] = tmp[i] * kLog2e;
+        }
+        if constexpr (BIAS == kBiasDecomposed64) {
+          // The row's 64 rel_w values (32 words of 16-bit pairs) are the same for every key tile: they are staged
+          // once per item in this thread's own row of the staging area (read back by this thread only, so no
+          // synchronisation), and the first pair of rel_h values is fetched; later pairs are fetched a step ahead.
+          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias2.ptr) + bias2_row);
+          uint32_t* stage = reinterpret_cast<uint32_t*>(sm.rel_stage[t][row_in_tile]);
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = __ldg(src + u);
+          rh_next0 = load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row);
+          rh_next1 = p.rel_kh > 1 ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + 1) : 0.f;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            stage[u * 4 + 0] = v[u].x;
+            stage[u * 4 + 1] = v[u].y;
+            stage[u * 4 + 2] = v[u].z;
+            stage[u * 4 + 3] = v[u].w;
+          }
+        }
         if constexpr (BIAS == kBiasDecomposed) {
           if (p.rel_staged) {  // this thread's rows, read back by this thread only: no synchronisation needed
             float* stage = sm.rel_stage[t][row_in_tile];
@@ -627,28 +683,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // Keys kv0 .. kv0+127 are (row 2j, all 64 columns) then (row 2j+1, all 64 columns) of the key grid.
           const bool is_half = p.bias2.dtype == 0;
           const int ih = kv0 >> 6;
-          const float rh0 = load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih) * kLog2e;
-          const float rh1 = (ih + 1 < p.rel_kh) ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih + 1) * kLog2e : 0.f;
-          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias2.ptr) + bias2_row);
+          const float rh0 = rh_next0 * kLog2e, rh1 = rh_next1 * kLog2e;
+          // The next step's pair, in flight behind this whole step.
+          rh_next0 = (ih + 2 < p.rel_kh) ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih + 2) : 0.f;
+          rh_next1 = (ih + 3 < p.rel_kh) ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih + 3) : 0.f;
+          const uint32_t* stage = reinterpret_cast<const uint32_t*>(sm.rel_stage[t][row_in_tile]);
 #pragma unroll
-          for (int ch = 0; ch < 2; ++ch) {  // 32 rel_w values at a time, used by columns ch*32.. and 64+ch*32..
-            uint4 v[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) v[u] = __ldg(src + ch * 4 + u);
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const uint32_t w4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 rw = unpack2(w4[e], is_half);
-                const int i = ch * 32 + u * 8 + e * 2;
-                s[i] = fmaf(s[i], c, fmaf(rw.x, kLog2e, rh0));
-                s[i + 1] = fmaf(s[i + 1], c, fmaf(rw.y, kLog2e, rh0));
-                s[i + 64] = fmaf(s[i + 64], c, fmaf(rw.x, kLog2e, rh1));
-                s[i + 65] = fmaf(s[i + 65], c, fmaf(rw.y, kLog2e, rh1));
-              }
-            }
+          for (int e = 0; e < 32; ++e) {  // one word = rel_w of columns 2e, 2e+1, used by keys 2e.. and 64+2e..
+            const float2 rw = unpack2(stage[e], is_half);
+            const int i = 2 * e;
+            const float2 cc = make_float2(c, c), ll = make_float2(kLog2e, kLog2e);
+            const float2 lo = ffma2(make_float2(s[i], s[i + 1]), cc, ffma2(rw, ll, make_float2(rh0, rh0)));
+            const float2 hi = ffma2(make_float2(s[i + 64], s[i + 65]), cc, ffma2(rw, ll, make_float2(rh1, rh1)));
+            s[i] = lo.x;
+            s[i + 1] = lo.y;
+            s[i + 64] = hi.x;
+            s[i + 65] = hi.y;
           }
+        } else if constexpr (BIAS == kBiasDecomposed14) {
+          if (j == 0) add_rel14<0>(s, sm.rel_stage[t][row_in_tile], c);
+          else add_rel14<kTileRows>(s, sm.rel_stage[t][row_in_tile], c);
         } else if constexpr (BIAS == kBiasDecomposed) {
           int ih = fast_div(kv0, p.magic_rel_kw);
           int iw = kv0 - ih * p.rel_kw;

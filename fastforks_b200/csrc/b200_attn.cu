@@ -255,6 +255,8 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
     if (a->rel_kw == 64 && a->rel_dtype != B200_ATTN_F32 && aligned16(a->rel_w) && a->rel_w_stride[0] % 8 == 0 &&
         a->rel_w_stride[1] % 8 == 0 && a->rel_w_stride[2] % 8 == 0)
       bias_mode = kBiasDecomposed64;
+    else if (a->rel_kh == 14 && a->rel_kw == 14)
+      bias_mode = kBiasDecomposed14;
   }
   cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&prm.status), g_status_word);
   if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(status word)");
@@ -273,6 +275,9 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
     case kBiasDecomposed64:
       return f16 ? launch<__half, kBiasDecomposed64>(a, prm, mq, mk, mv, stream)
                  : launch<__nv_bfloat16, kBiasDecomposed64>(a, prm, mq, mk, mv, stream);
+    case kBiasDecomposed14:
+      return f16 ? launch<__half, kBiasDecomposed14>(a, prm, mq, mk, mv, stream)
+                 : launch<__nv_bfloat16, kBiasDecomposed14>(a, prm, mq, mk, mv, stream);
     default:
       return f16 ? launch<__half, kBiasDecomposed>(a, prm, mq, mk, mv, stream)
                  : launch<__nv_bfloat16, kBiasDecomposed>(a, prm, mq, mk, mv, stream);

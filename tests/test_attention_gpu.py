@@ -186,6 +186,26 @@ def test_decomposed_bias_sam_shapes(hw: tuple[int, int], b: int, h: int) -> None
     assert_close(got.float().cpu().numpy(), ref, unit_scale=True)
 
 
+@pytest.mark.parametrize(
+    ("hw", "nq", "dtype", "rel_dtype"),
+    [((14, 14), 77, "fp16", torch.float32), ((14, 14), 300, "bf16", torch.bfloat16), ((64, 64), 130, "bf16", torch.bfloat16)],
+)
+def test_decomposed_bias_fast_paths_cross_length(hw: tuple[int, int], nq: int, dtype: str, rel_dtype: torch.dtype) -> None:
+    """The 14 x 14 and 64-wide forms of the decomposed bias with a query count that differs from the key count
+    (one-tile and three-tile items) and with tables of another type than q / k / v."""
+    dt = DTYPES[dtype]
+    gen = torch.Generator().manual_seed(nq)
+    b, h, nk = 2, 2, hw[0] * hw[1]
+    q = torch.randn(b, h, nq, 64, generator=gen).to(dt).cuda()
+    k, v = (torch.randn(b, h, nk, 64, generator=gen).to(dt).cuda() for _ in range(2))
+    rel_h = torch.randn(b, h, nq, hw[0], generator=gen).to(rel_dtype)
+    rel_w = torch.randn(b, h, nq, hw[1], generator=gen).to(rel_dtype)
+    got = ff.scaled_dot_product_attention(q, k, v, rel=(rel_h.cuda(), rel_w.cuda()))
+    args = [t.float().cpu().numpy() for t in (q, k, v)]
+    ref = c_oracle.attention(*args, 0.125, rel=(rel_h.float().numpy(), rel_w.float().numpy()), threads=8)
+    assert_close(got.float().cpu().numpy(), ref, unit_scale=True)
+
+
 def test_extreme_range_inputs_give_the_fp32_result() -> None:
     """The reference's overflow case (tests/test_flash64_guard.py:175-199): q[..., 0] = k[..., 0] = 400 overflows fp16
     accumulators there and needs its fallback chain; here accumulation is fp32, so the first answer is the fp32 one."""
