@@ -35,7 +35,8 @@ constexpr int kHeadDim = 64;                          // the only head dim of th
 constexpr int kTileBytes = kTileRows * kHeadDim * 2;  // one Q / K / V tile in shared memory
 constexpr int kLoaderWarp = 8;
 constexpr int kMmaWarp = 9;                           // warps 9 and 10 issue the MMAs of query tile 0 and 1
-constexpr int kThreads = 384;                         // 2 softmax warpgroups + 1 warpgroup of helpers (1 idle warp)
+constexpr int kStoreWarp = 11;                        // issues the TMA stores of the output tiles
+constexpr int kThreads = 384;                         // 2 softmax warpgroups + 1 warpgroup of helpers
 constexpr int kSoftmaxRegs = 224, kHelperRegs = 56;   // per-thread register budgets after the hand-over
 constexpr int kLaunchRegs = 168;                      // what a 384-thread CTA gets per thread at launch
 // setmaxnreg.inc blocks until the CTA's pool holds the registers: the budgets must fit what the launch
@@ -49,18 +50,19 @@ constexpr uint32_t kTmemS = 0, kTmemO = 256, kTmemP = 384;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;             // log2 units: P stays below 2^8 between rescales
 
-enum : uint32_t { kStatusLoader = 1, kStatusMma = 2, kStatusSoftmax = 4 };
+enum : uint32_t { kStatusLoader = 1, kStatusMma = 2, kStatusSoftmax = 4, kStatusStore = 16 };  // 8: the wait self-test
 
 // Development aid, compiled out of the shipped library: with -DB200_TRACE one lane per role of CTA 0 writes
 // clock stamps to AttnParams::trace so that the pipeline's timeline can be read back.
 #ifdef B200_TRACE
-// Stamps go to shared memory (one store, no divergent global access) and are copied out when the CTA leaves.
+// Stamps go to shared memory (one store, no divergent global access) and are copied out when the CTA leaves. They
+// borrow the bias staging area, so only the kernels without a bias can be traced.
 #define B200_STAMP(role, iter, slot)                                               \
   do {                                                                             \
     if (lane == 0 && (iter) < 32) {                                                \
       uint32_t t_;                                                                 \
       asm volatile("mov.u32 %0, %%clock;" : "=r"(t_));                             \
-      sm.trace[((role) * 32 + (iter)) * 8 + (slot)] = t_;                          \
+      reinterpret_cast<uint32_t*>(sm.rel_stage)[((role) * 32 + (iter)) * 8 + (slot)] = t_; \
     }                                                                              \
   } while (0)
 #else
@@ -103,6 +105,7 @@ struct alignas(1024) AttnSmem {
   uint8_t q[2][2][kTileBytes];  // [query-tile slot][item parity]: the next item's Q is loaded while this one computes
   uint8_t k[kStagesK][kTileBytes];
   uint8_t v[kStagesV][kTileBytes];
+  uint8_t o_stage[2][kTileBytes];  // an item's output tile per query-tile slot, in the TMA tile layout (128-byte swizzle)
   uint64_t q_full[2][2];   // Q_t of an item has landed                      (TMA)
   uint64_t q_empty[2][2];  // that item's last Q_t K^T has finished          (MMA commit)
   uint64_t k_full[kStagesK], k_empty[kStagesK];
@@ -113,11 +116,10 @@ struct alignas(1024) AttnSmem {
   uint64_t pv_done[2];  // O_t += P_t(j) V(j) has finished                 (MMA commit)
   uint64_t o_free[2];   // the item's O_t has been read by its epilogue     (4 softmax warps)
   uint64_t turn[2];     // the other warpgroup is half way through its exponentials: t may start (4 warps)
+  uint64_t o_staged[2];      // the item's output tile t is in o_stage[t]           (4 softmax warps)
+  uint64_t o_stage_free[2];  // the TMA store of that tile has read o_stage[t]       (store thread)
   uint32_t tmem_base;
   uint32_t abort;
-#ifdef B200_TRACE
-  uint32_t trace[12 * 32 * 8];
-#endif
   float rel_stage[2][kTileRows][kRelStageWords];  // each softmax thread's own rel_h | rel_w row, times log2(e)
 };
 
@@ -238,6 +240,8 @@ __device__ __forceinline__ void add_rel14(float* s, const float* stage, float c)
   }
 }
 
+static_assert(sizeof(AttnSmem) + 1024 <= 227 * 1024, "shared memory of one CTA");
+
 // One unit of work: one or two 128-row query tiles of one (batch, head).
 struct WorkItem {
   int b, h, q_row0, n_tiles;
@@ -272,7 +276,7 @@ __device__ __forceinline__ WorkItem decode_item(const AttnParams& p, int item_id
 template <typename T, int BIAS>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   AttnSmem& sm = *reinterpret_cast<AttnSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -300,6 +304,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&sm.pv_done[i], 1);
       mbar_init(&sm.o_free[i], 4);
       mbar_init(&sm.turn[i], 4);
+      mbar_init(&sm.o_staged[i], 4);
+      mbar_init(&sm.o_stage_free[i], 1);
     }
     for (int i = 0; i < kStagesK; ++i) {
       mbar_init(&sm.k_full[i], 1);
@@ -311,7 +317,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     sm.abort = 0;
 #ifdef B200_TRACE
-    for (int i = 0; i < 12 * 32 * 8; ++i) sm.trace[i] = 0;
+    for (int i = 0; i < 12 * 32 * 8; ++i) reinterpret_cast<uint32_t*>(sm.rel_stage)[i] = 0;
 #endif
     mbar_init_fence();
   }
@@ -323,6 +329,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_o);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -505,6 +512,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       __syncwarp();
+    } else if (warp == kStoreWarp) {
+      // ======================= output stores ====================================================
+      // One thread sends each finished output tile from its staging buffer to global memory with a TMA store (rows
+      // past the end of the sequence are clipped by the tensor map) and hands the buffer back once it has been read.
+      if (lane == 0) {
+        bool ok = true;
+        for (int it = 0; it < my_items && ok; ++it) {
+          const WorkItem w = decode_item(p, blockIdx.x + it * gridDim.x);
+          for (int t = 0; t < w.n_tiles && ok; ++t) {
+            // Slot 1's items are a prefix of the CTA's list, so this is the it-th use of either slot's buffer.
+            ok = mbar_wait(&sm.o_staged[t], it & 1, abort_flag);
+            if (!ok) break;
+            tma_store_4d(&tm_o, sm.o_stage[t], 0, w.q_row0 + t * kTileRows, w.h, w.b);
+            tma_store_commit();
+          }
+          // The buffers are not needed again before the next item's epilogue: one wait for both stores.
+          tma_store_wait_read<0>();
+          for (int t = 0; t < w.n_tiles && ok; ++t) mbar_arrive(&sm.o_stage_free[t]);
+        }
+        // Every store has read its buffer by now (the wait above); the writes themselves complete with the kernel.
+        if (!ok) {
+          if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusStore);
+        }
+      }
+      __syncwarp();
     }
   } else {
     // ======================= softmax warpgroups ================================================
@@ -525,8 +557,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     bool pend = false;
     uint32_t pend_phase = 0;
     float pend_inv = 0.f;
-    T* pend_dst = nullptr;
-    // O_t / l -> global for the pending item; frees O_t for the next item's first P V.
+    int pend_it = 0;
+    // O_t / l -> staging buffer -> (store thread) global for the pending item; frees O_t for the next item's first P V.
+    // Each thread writes its 128-byte row as eight 16-byte chunks at the positions of the 128-byte swizzle.
     auto finish_item = [&]() -> bool {
       if (!__all_sync(0xffffffffu, mbar_wait(&sm.pv_done[t], pend_phase, abort_flag))) return false;
       tc_fence_after_sync();
@@ -534,17 +567,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld_x64(o_addr, reinterpret_cast<uint32_t*>(o));
       tc_fence_before_sync();
       warp_arrive(&sm.o_free[t], lane);
-      if (pend_dst != nullptr) {
+      // The buffer's previous tile (the item before the pending one) must have been read by its store.
+      if (pend_it > 0 && !__all_sync(0xffffffffu, mbar_wait(&sm.o_stage_free[t], (pend_it - 1) & 1, abort_flag)))
+        return false;
+      const uint32_t row = smem_u32(sm.o_stage[t]) + row_in_tile * (kHeadDim * 2);
 #pragma unroll
-        for (int ch = 0; ch < kHeadDim / 8; ++ch) {
-          uint4 val;
-          val.x = pack2<T>(o[ch * 8 + 0] * pend_inv, o[ch * 8 + 1] * pend_inv);
-          val.y = pack2<T>(o[ch * 8 + 2] * pend_inv, o[ch * 8 + 3] * pend_inv);
-          val.z = pack2<T>(o[ch * 8 + 4] * pend_inv, o[ch * 8 + 5] * pend_inv);
-          val.w = pack2<T>(o[ch * 8 + 6] * pend_inv, o[ch * 8 + 7] * pend_inv);
-          *reinterpret_cast<uint4*>(pend_dst + ch * 8) = val;
-        }
+      for (int ch = 0; ch < kHeadDim / 8; ++ch) {
+        uint4 val;
+        val.x = pack2<T>(o[ch * 8 + 0] * pend_inv, o[ch * 8 + 1] * pend_inv);
+        val.y = pack2<T>(o[ch * 8 + 2] * pend_inv, o[ch * 8 + 3] * pend_inv);
+        val.z = pack2<T>(o[ch * 8 + 4] * pend_inv, o[ch * 8 + 5] * pend_inv);
+        val.w = pack2<T>(o[ch * 8 + 6] * pend_inv, o[ch * 8 + 7] * pend_inv);
+        st_shared_v4(row + ((ch ^ (row_in_tile & 7)) << 4), val);
       }
+      fence_proxy_async_smem();  // the TMA store reads what these generic-proxy stores wrote
+      warp_arrive(&sm.o_staged[t], lane);
       pend = false;
       return true;
     };
@@ -777,11 +814,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const float2 c2 = (BIAS == kBiasNone) ? make_float2(c, c) : make_float2(1.f, 1.f);
         float nm = -m_use;
         uint32_t pk[kTileRows / 2];
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        // Midpoint of the section: let the other warpgroup start (the rest of the section reads `nm` through the
+        // arrival, which pins it in the instruction stream) and issue the tests of the barriers needed next.
+        auto midpoint = [&]() {
+          if (pingpong) warp_arrive_pinned(&sm.turn[t ^ 1], lane, nm);
+          pv_early = (j > 0) ? mbar_test_wait(&sm.pv_done[t], (step - 1) & 1) : true;
+          s_early = mbar_test_wait(&sm.s_full[t], (step + 1) & 1);  // the next step's S (unused after the last step)
+        };
+        // Exponentials of 32 * CHUNKS columns from column 32 * FIRST on.
+        auto exp_columns = [&](auto first, auto chunks) {
+          constexpr int kFirst = decltype(first)::value * 32, kCount = decltype(chunks)::value * 32;
           const float2 nm2 = make_float2(nm, nm);
 #pragma unroll
-          for (int i = half * (kTileRows / 2); i < (half + 1) * (kTileRows / 2); i += 4) {
+          for (int i = kFirst; i < kFirst + kCount; i += 4) {
             const float2 xa = ffma2(make_float2(s[i], s[i + 1]), c2, nm2);
             const float2 xb = ffma2(make_float2(s[i + 2], s[i + 3]), c2, nm2);
             const float2 pa = make_float2(fast_exp2(xa.x), fast_exp2(xa.y));
@@ -791,13 +836,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             pk[i / 2] = pack2<T>(pa.x, pa.y);
             pk[i / 2 + 1] = pack2<T>(pb.x, pb.y);
           }
-          // Midpoint: let the other warpgroup start. The second half reads `nm` through the arrival.
-          if (half == 0 && pingpong) warp_arrive_pinned(&sm.turn[t ^ 1], lane, nm);
-          if (half == 0) {
-            pv_early = (j > 0) ? mbar_test_wait(&sm.pv_done[t], (step - 1) & 1) : true;
-            s_early = mbar_test_wait(&sm.s_full[t], (step + 1) & 1);  // the next step's S (unused after the last step)
-          }
-        }
+        };
+        using std::integral_constant;
+        exp_columns(integral_constant<int, 0>{}, integral_constant<int, 2>{});
+        midpoint();
+        exp_columns(integral_constant<int, 2>{}, integral_constant<int, 2>{});
         if ((warp & 3) == 0) B200_STAMP(t, step, 3);
         l_sum += (l2a.x + l2a.y) + (l2b.x + l2b.y);
 
@@ -841,8 +884,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       pend = true;
       pend_phase = (g + kv_tiles - 1) & 1;
       pend_inv = 1.f / l_sum;
-      pend_dst = row_valid ? reinterpret_cast<T*>(p.o) + b * p.o_sb + static_cast<int64_t>(q_row) * p.o_sn + h * p.o_sh
-                           : nullptr;
+      pend_it = it;
       g += kv_tiles;
       if (w.n_tiles == 2) gp += kv_tiles;
     }
@@ -857,7 +899,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
 #ifdef B200_TRACE
   if (blockIdx.x == 0 && p.trace != nullptr)
-    for (int i = threadIdx.x; i < 12 * 32 * 8; i += kThreads) p.trace[i] = sm.trace[i];
+    for (int i = threadIdx.x; i < 12 * 32 * 8; i += kThreads) p.trace[i] = reinterpret_cast<uint32_t*>(sm.rel_stage)[i];
 #endif
   if (warp == kMmaWarp) {
     tc_fence_after_sync();

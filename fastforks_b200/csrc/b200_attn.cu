@@ -180,7 +180,7 @@ int validate(const B200AttnArgs* a, int* bias_mode, int* schedule) {
 
 template <typename T, int BIAS>
 int launch(const B200AttnArgs* a, const AttnParams& prm, const CUtensorMap& mq, const CUtensorMap& mk,
-           const CUtensorMap& mv, cudaStream_t stream) {
+           const CUtensorMap& mv, const CUtensorMap& mo, cudaStream_t stream) {
   auto kernel = attn_fwd_kernel<T, BIAS>;
   constexpr int smem = static_cast<int>(sizeof(AttnSmem)) + 1024;
   // The opt-in is per device and per kernel; setting it again is cheap and keeps this path stateless.
@@ -193,7 +193,7 @@ int launch(const B200AttnArgs* a, const AttnParams& prm, const CUtensorMap& mq, 
   if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(multiprocessor count)");
   const long long items = static_cast<long long>(prm.items_per_head) * a->batch * a->heads;
   const unsigned grid = static_cast<unsigned>(items < sms ? items : sms);
-  kernel<<<grid, kThreads, smem, stream>>>(mq, mk, mv, prm);
+  kernel<<<grid, kThreads, smem, stream>>>(mq, mk, mv, mo, prm);
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "attention kernel launch");
   return B200_ATTN_OK;
@@ -216,10 +216,11 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
   if (rc != B200_ATTN_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
 
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   if ((rc = make_tile_map(&mq, a->q, a->dtype, a->batch, a->heads, a->q_tokens, a->q_stride, "q"))) return rc;
   if ((rc = make_tile_map(&mk, a->k, a->dtype, a->batch, a->heads, a->kv_tokens, a->k_stride, "k"))) return rc;
   if ((rc = make_tile_map(&mv, a->v, a->dtype, a->batch, a->heads, a->kv_tokens, a->v_stride, "v"))) return rc;
+  if ((rc = make_tile_map(&mo, a->o, a->dtype, a->batch, a->heads, a->q_tokens, a->o_stride, "o"))) return rc;
 
   AttnParams prm;
   std::memset(&prm, 0, sizeof(prm));
@@ -267,20 +268,20 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
   const bool f16 = a->dtype == B200_ATTN_F16;
   switch (bias_mode) {
     case kBiasNone:
-      return f16 ? launch<__half, kBiasNone>(a, prm, mq, mk, mv, stream)
-                 : launch<__nv_bfloat16, kBiasNone>(a, prm, mq, mk, mv, stream);
+      return f16 ? launch<__half, kBiasNone>(a, prm, mq, mk, mv, mo, stream)
+                 : launch<__nv_bfloat16, kBiasNone>(a, prm, mq, mk, mv, mo, stream);
     case kBiasDense:
-      return f16 ? launch<__half, kBiasDense>(a, prm, mq, mk, mv, stream)
-                 : launch<__nv_bfloat16, kBiasDense>(a, prm, mq, mk, mv, stream);
+      return f16 ? launch<__half, kBiasDense>(a, prm, mq, mk, mv, mo, stream)
+                 : launch<__nv_bfloat16, kBiasDense>(a, prm, mq, mk, mv, mo, stream);
     case kBiasDecomposed64:
-      return f16 ? launch<__half, kBiasDecomposed64>(a, prm, mq, mk, mv, stream)
-                 : launch<__nv_bfloat16, kBiasDecomposed64>(a, prm, mq, mk, mv, stream);
+      return f16 ? launch<__half, kBiasDecomposed64>(a, prm, mq, mk, mv, mo, stream)
+                 : launch<__nv_bfloat16, kBiasDecomposed64>(a, prm, mq, mk, mv, mo, stream);
     case kBiasDecomposed14:
-      return f16 ? launch<__half, kBiasDecomposed14>(a, prm, mq, mk, mv, stream)
-                 : launch<__nv_bfloat16, kBiasDecomposed14>(a, prm, mq, mk, mv, stream);
+      return f16 ? launch<__half, kBiasDecomposed14>(a, prm, mq, mk, mv, mo, stream)
+                 : launch<__nv_bfloat16, kBiasDecomposed14>(a, prm, mq, mk, mv, mo, stream);
     default:
-      return f16 ? launch<__half, kBiasDecomposed>(a, prm, mq, mk, mv, stream)
-                 : launch<__nv_bfloat16, kBiasDecomposed>(a, prm, mq, mk, mv, stream);
+      return f16 ? launch<__half, kBiasDecomposed>(a, prm, mq, mk, mv, mo, stream)
+                 : launch<__nv_bfloat16, kBiasDecomposed>(a, prm, mq, mk, mv, mo, stream);
   }
 }
 

@@ -149,6 +149,9 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
 // ---------------------------------------------------------------------------------------------
 // Proxy / tcgen05 fences
 // ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
