@@ -116,7 +116,7 @@ int b200_attn_query(const B200AttnArgs* args, int32_t* schedule);
 /*
  * Reads and clears the device-side error word of the current device (synchronises that device).
  * 0 = every wait inside the kernels completed.  Non-zero: a kernel gave up a bounded wait on a barrier and
- * returned early, its output is invalid; the bits say which role (1 loader, 2 MMA issuer, 4 softmax).
+ * returned early, its output is invalid; the bits say which role (1 loader, 2 MMA issuer, 4 softmax, 16 output store).
  * The reference has no counterpart: its kernels contain no waits on asynchronous units.
  */
 int b200_attn_status(uint32_t* status);
