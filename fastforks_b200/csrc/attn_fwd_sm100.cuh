@@ -552,7 +552,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     int gp = 0;       // steps so far in items where both warpgroups work (phases of the turn barriers)
     bool ok = true;
     bool bad = false;  // this lane gave up a wait since the last vote
-    bool s_early = false, pv_early = false;  // early barrier tests (see the step loop)
+    bool s_early = false, pv_early = false, stage_early = false;  // early barrier tests (see the step loop)
     // Epilogue of the previous item, still to be done: its last P V phase, 1 / row sum, output row (or null).
     bool pend = false;
     uint32_t pend_phase = 0;
@@ -560,15 +560,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     int pend_it = 0;
     // O_t / l -> staging buffer -> (store thread) global for the pending item; frees O_t for the next item's first P V.
     // Each thread writes its 128-byte row as eight 16-byte chunks at the positions of the 128-byte swizzle.
-    auto finish_item = [&]() -> bool {
-      if (!__all_sync(0xffffffffu, mbar_wait(&sm.pv_done[t], pend_phase, abort_flag))) return false;
+    // `pv_tested`, `stage_tested`: results of early tests of the two barriers (false = not tested or still pending).
+    auto finish_item = [&](bool pv_tested, bool stage_tested) -> bool {
+      if (!__all_sync(0xffffffffu, pv_tested || mbar_wait(&sm.pv_done[t], pend_phase, abort_flag))) return false;
       tc_fence_after_sync();
       float o[kHeadDim];
       tmem_ld_x64(o_addr, reinterpret_cast<uint32_t*>(o));
       tc_fence_before_sync();
       warp_arrive(&sm.o_free[t], lane);
       // The buffer's previous tile (the item before the pending one) must have been read by its store.
-      if (pend_it > 0 && !__all_sync(0xffffffffu, mbar_wait(&sm.o_stage_free[t], (pend_it - 1) & 1, abort_flag)))
+      if (pend_it > 0 &&
+          !__all_sync(0xffffffffu, stage_tested || mbar_wait(&sm.o_stage_free[t], (pend_it - 1) & 1, abort_flag)))
         return false;
       const uint32_t row = smem_u32(sm.o_stage[t]) + row_in_tile * (kHeadDim * 2);
 #pragma unroll
@@ -818,7 +820,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // arrival, which pins it in the instruction stream) and issue the tests of the barriers needed next.
         auto midpoint = [&]() {
           if (pingpong) warp_arrive_pinned(&sm.turn[t ^ 1], lane, nm);
-          pv_early = (j > 0) ? mbar_test_wait(&sm.pv_done[t], (step - 1) & 1) : true;
+          // On an item's first tile the P V in question is the last one of the pending item (same barrier, and
+          // (step - 1) & 1 is that item's last phase), waited for by its epilogue together with the staging buffer.
+          pv_early = (j > 0 || pend) ? mbar_test_wait(&sm.pv_done[t], (step - 1) & 1) : true;
+          stage_early = (j == 0 && pend && pend_it > 0) ? mbar_test_wait(&sm.o_stage_free[t], (pend_it - 1) & 1) : false;
           s_early = mbar_test_wait(&sm.s_full[t], (step + 1) & 1);  // the next step's S (unused after the last step)
         };
         // Exponentials of 32 * CHUNKS columns from column 32 * FIRST on.
@@ -850,7 +855,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // its epilogue hides behind this item's first exponentials instead of stalling the pipeline.
         if (j == 0) {
           if (pend) {
-            ok = finish_item();
+            ok = finish_item(pv_early, stage_early);
             if (!ok) break;
           }
         } else {
@@ -888,7 +893,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       g += kv_tiles;
       if (w.n_tiles == 2) gp += kv_tiles;
     }
-    if (ok && pend) ok = finish_item();
+    if (ok && pend) ok = finish_item(false, false);
     if (!ok && lane == 0) {
       if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusSoftmax);
     }
