@@ -727,18 +727,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           rh_next0 = (ih + 2 < p.rel_kh) ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih + 2) : 0.f;
           rh_next1 = (ih + 3 < p.rel_kh) ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih + 3) : 0.f;
           const uint32_t* stage = reinterpret_cast<const uint32_t*>(sm.rel_stage[t][row_in_tile]);
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {  // one word = rel_w of columns 2e, 2e+1, used by keys 2e.. and 64+2e..
-            const float2 rw = unpack2(stage[e], is_half);
-            const int i = 2 * e;
+          // The table's type is decided once per step, not once per word.
+          auto add_rel64 = [&](auto half_tag) {
+            constexpr bool kHalf = decltype(half_tag)::value;
             const float2 cc = make_float2(c, c), ll = make_float2(kLog2e, kLog2e);
-            const float2 lo = ffma2(make_float2(s[i], s[i + 1]), cc, ffma2(rw, ll, make_float2(rh0, rh0)));
-            const float2 hi = ffma2(make_float2(s[i + 64], s[i + 65]), cc, ffma2(rw, ll, make_float2(rh1, rh1)));
-            s[i] = lo.x;
-            s[i + 1] = lo.y;
-            s[i + 64] = hi.x;
-            s[i + 65] = hi.y;
-          }
+            const float2 r0 = make_float2(rh0, rh0), r1 = make_float2(rh1, rh1);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {  // one word = rel_w of columns 2e, 2e+1, used by keys 2e.. and 64+2e..
+              const float2 rw = unpack2(stage[e], kHalf);
+              const int i = 2 * e;
+              const float2 lo = ffma2(make_float2(s[i], s[i + 1]), cc, ffma2(rw, ll, r0));
+              const float2 hi = ffma2(make_float2(s[i + 64], s[i + 65]), cc, ffma2(rw, ll, r1));
+              s[i] = lo.x;
+              s[i + 1] = lo.y;
+              s[i + 64] = hi.x;
+              s[i + 65] = hi.y;
+            }
+          };
+          if (is_half) add_rel64(std::true_type{});
+          else add_rel64(std::false_type{});
         } else if constexpr (BIAS == kBiasDecomposed14) {
           if (j == 0) add_rel14<0>(s, sm.rel_stage[t][row_in_tile], c);
           else add_rel14<kTileRows>(s, sm.rel_stage[t][row_in_tile], c);
