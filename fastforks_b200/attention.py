@@ -11,6 +11,7 @@ raises `KernelUnavailableError`.
 from __future__ import annotations
 
 import ctypes
+import threading
 from typing import TYPE_CHECKING
 
 import torch
@@ -113,6 +114,63 @@ def _bias_view(name: str, t: torch.Tensor, shape: Sequence[int], q: torch.Tensor
         raise ValueError(msg) from e
 
 
+# Launch descriptions already checked once, per thread: geometry key -> (args struct, output shape). A ViT calls the
+# operator with the same views in every block and every forward; for launch-bound shapes (one image of 197 tokens) the
+# checks and the ctypes set-up of a call cost more than the kernel, so a repeated geometry only has its four
+# pointers and the scale filled in again. The key holds everything `check_operands` looks at.
+_PREPARED = threading.local()
+_PREPARED_LIMIT = 256
+
+
+def _geometry_key(q, k, v, layout, out, schedule):  # noqa: ANN001, ANN202
+    return (
+        q.dtype, k.dtype, v.dtype, q.device, k.device, v.device, layout, schedule, q.shape, k.shape, v.shape,
+        q.stride(), k.stride(), v.stride(),
+        None if out is None else (out.dtype, out.device, out.shape, out.stride()),
+    )  # fmt: skip
+
+
+def _launch_prepared(q, k, v, scale, layout, out, schedule):  # noqa: ANN001, ANN202, PLR0913
+    """Launch from a remembered description of this geometry; None when there is none (the full path then runs)."""
+    table = getattr(_PREPARED, "table", None)
+    if table is None:
+        return None
+    try:
+        entry = table.get(_geometry_key(q, k, v, layout, out, schedule))
+    except (AttributeError, TypeError):  # not tensors: let the full path raise its ValueError
+        return None
+    if entry is None:
+        return None
+    if (q.requires_grad or k.requires_grad or v.requires_grad) and torch.is_grad_enabled():
+        return None
+    a, o_shape, index = entry
+    if index != torch.cuda.current_device():
+        return None
+    if out is None:
+        o = torch.empty(o_shape, device=q.device, dtype=q.dtype)
+        out = o.transpose(1, 2) if layout == "bhnd" else o
+    a.q, a.k, a.v, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    a.scale = float(HEAD_DIM**-0.5 if scale is None else scale)
+    code = _lib.library().b200_attn_fwd(ctypes.byref(a), torch._C._cuda_getCurrentRawStream(index))  # noqa: SLF001
+    if code != _lib.OK:
+        _lib.raise_for_code(code, "attention")
+    return out
+
+
+def _remember(a, q, k, v, out, layout, schedule) -> None:  # noqa: ANN001, PLR0913
+    """Keep the checked description `a` of this geometry for the calling thread (`out` as the caller gave it)."""
+    index = q.device.index
+    if index is None or index != torch.cuda.current_device():
+        return
+    table = getattr(_PREPARED, "table", None)
+    if table is None:
+        table = _PREPARED.table = {}
+    if len(table) >= _PREPARED_LIMIT:
+        table.clear()
+    copy = _lib.B200AttnArgs.from_buffer_copy(a)
+    table[_geometry_key(q, k, v, layout, out, schedule)] = (copy, (a.batch, a.q_tokens, a.heads, HEAD_DIM), index)
+
+
 def attention(  # noqa: PLR0913
     q: torch.Tensor,
     k: torch.Tensor,
@@ -150,6 +208,10 @@ def attention(  # noqa: PLR0913
         KernelUnavailableError: The CUDA library is not built or does not load.
         RuntimeError: A CUDA error at launch.
     """
+    if bias is None and rel is None:
+        done = _launch_prepared(q, k, v, scale, layout, out, schedule)
+        if done is not None:
+            return done
     check_operands(q, k, v, layout, out)
     if schedule not in _SCHEDULES:
         msg = f"attention: schedule {schedule!r}: expected one of {tuple(_SCHEDULES)}"
@@ -160,6 +222,7 @@ def attention(  # noqa: PLR0913
     lib = _lib.library()
     b, n, h = _sizes(q, layout)
     _, nk, _ = _sizes(k, layout)
+    given_out = out
     if out is None:
         o = torch.empty((b, n, h, HEAD_DIM), device=q.device, dtype=q.dtype)
         out = o.transpose(1, 2) if layout == "bhnd" else o
@@ -199,6 +262,8 @@ def attention(  # noqa: PLR0913
         a.rel_h_stride[:] = rh.stride()[:3]
         a.rel_w_stride[:] = rw.stride()[:3]
 
+    if bias is None and rel is None:
+        _remember(a, q, k, v, given_out, layout, schedule)
     index = q.device.index if q.device.index is not None else torch.cuda.current_device()
     if index != torch.cuda.current_device():
         with torch.cuda.device(index):

@@ -5,12 +5,14 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 #include "attn_fwd_sm100.cuh"
 
@@ -178,23 +180,59 @@ int validate(const B200AttnArgs* a, int* bias_mode, int* schedule) {
   return B200_ATTN_OK;
 }
 
+// What a launch needs to know about the current device, looked up once per device: the SM count, the address of the
+// status word and which kernels already have their shared-memory opt-in (the opt-in is per device and per kernel).
+// The runtime calls behind these cost more than the rest of the host path of a launch-bound call.
+constexpr int kMaxDevices = 64;
+constexpr int kKernelForms = 10;  // 2 dtypes x 5 bias forms
+struct DeviceState {
+  std::atomic<bool> ready{false};
+  int sms = 0;
+  uint32_t* status = nullptr;
+  std::atomic<bool> opted_in[kKernelForms];
+};
+DeviceState g_devices[kMaxDevices];
+std::mutex g_devices_mutex;
+
+int device_state(DeviceState** out) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (device < 0 || device >= kMaxDevices)
+    return fail(B200_ATTN_UNSUPPORTED, "device ordinal %d: at most %d devices are supported", device, kMaxDevices);
+  DeviceState& d = g_devices[device];
+  if (!d.ready.load(std::memory_order_acquire)) {
+    std::lock_guard<std::mutex> lock(g_devices_mutex);
+    if (!d.ready.load(std::memory_order_relaxed)) {
+      e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, device);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(multiprocessor count)");
+      e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status), g_status_word);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(status word)");
+      for (auto& f : d.opted_in) f.store(false, std::memory_order_relaxed);
+      d.ready.store(true, std::memory_order_release);
+    }
+  }
+  *out = &d;
+  return B200_ATTN_OK;
+}
+
 template <typename T, int BIAS>
-int launch(const B200AttnArgs* a, const AttnParams& prm, const CUtensorMap& mq, const CUtensorMap& mk,
-           const CUtensorMap& mv, const CUtensorMap& mo, cudaStream_t stream) {
+int launch(const B200AttnArgs* a, const AttnParams& prm, DeviceState& dev, const CUtensorMap& mq,
+           const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, cudaStream_t stream) {
   auto kernel = attn_fwd_kernel<T, BIAS>;
   constexpr int smem = static_cast<int>(sizeof(AttnSmem)) + 1024;
-  // The opt-in is per device and per kernel; setting it again is cheap and keeps this path stateless.
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(shared memory)");
+  constexpr int form = BIAS * 2 + (std::is_same<T, __half>::value ? 0 : 1);
+  static_assert(form < kKernelForms, "kernel form index");
+  if (!dev.opted_in[form].load(std::memory_order_acquire)) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(shared memory)");
+    dev.opted_in[form].store(true, std::memory_order_release);
+  }
   // Persistent CTAs: one per SM (shared memory and tensor memory allow no more), fewer when there is less work.
-  int device = 0, sms = 0;
-  e = cudaGetDevice(&device);
-  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(multiprocessor count)");
   const long long items = static_cast<long long>(prm.items_per_head) * a->batch * a->heads;
-  const unsigned grid = static_cast<unsigned>(items < sms ? items : sms);
+  const unsigned grid = static_cast<unsigned>(items < dev.sms ? items : dev.sms);
   kernel<<<grid, kThreads, smem, stream>>>(mq, mk, mv, mo, prm);
-  e = cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "attention kernel launch");
   return B200_ATTN_OK;
 }
@@ -259,8 +297,9 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
     else if (a->rel_kh == 14 && a->rel_kw == 14)
       bias_mode = kBiasDecomposed14;
   }
-  cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&prm.status), g_status_word);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(status word)");
+  DeviceState* dev = nullptr;
+  if ((rc = device_state(&dev))) return rc;
+  prm.status = dev->status;
 
 #ifdef B200_TRACE
   prm.trace = g_trace_buffer;
@@ -268,20 +307,20 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
   const bool f16 = a->dtype == B200_ATTN_F16;
   switch (bias_mode) {
     case kBiasNone:
-      return f16 ? launch<__half, kBiasNone>(a, prm, mq, mk, mv, mo, stream)
-                 : launch<__nv_bfloat16, kBiasNone>(a, prm, mq, mk, mv, mo, stream);
+      return f16 ? launch<__half, kBiasNone>(a, prm, *dev, mq, mk, mv, mo, stream)
+                 : launch<__nv_bfloat16, kBiasNone>(a, prm, *dev, mq, mk, mv, mo, stream);
     case kBiasDense:
-      return f16 ? launch<__half, kBiasDense>(a, prm, mq, mk, mv, mo, stream)
-                 : launch<__nv_bfloat16, kBiasDense>(a, prm, mq, mk, mv, mo, stream);
+      return f16 ? launch<__half, kBiasDense>(a, prm, *dev, mq, mk, mv, mo, stream)
+                 : launch<__nv_bfloat16, kBiasDense>(a, prm, *dev, mq, mk, mv, mo, stream);
     case kBiasDecomposed64:
-      return f16 ? launch<__half, kBiasDecomposed64>(a, prm, mq, mk, mv, mo, stream)
-                 : launch<__nv_bfloat16, kBiasDecomposed64>(a, prm, mq, mk, mv, mo, stream);
+      return f16 ? launch<__half, kBiasDecomposed64>(a, prm, *dev, mq, mk, mv, mo, stream)
+                 : launch<__nv_bfloat16, kBiasDecomposed64>(a, prm, *dev, mq, mk, mv, mo, stream);
     case kBiasDecomposed14:
-      return f16 ? launch<__half, kBiasDecomposed14>(a, prm, mq, mk, mv, mo, stream)
-                 : launch<__nv_bfloat16, kBiasDecomposed14>(a, prm, mq, mk, mv, mo, stream);
+      return f16 ? launch<__half, kBiasDecomposed14>(a, prm, *dev, mq, mk, mv, mo, stream)
+                 : launch<__nv_bfloat16, kBiasDecomposed14>(a, prm, *dev, mq, mk, mv, mo, stream);
     default:
-      return f16 ? launch<__half, kBiasDecomposed>(a, prm, mq, mk, mv, mo, stream)
-                 : launch<__nv_bfloat16, kBiasDecomposed>(a, prm, mq, mk, mv, mo, stream);
+      return f16 ? launch<__half, kBiasDecomposed>(a, prm, *dev, mq, mk, mv, mo, stream)
+                 : launch<__nv_bfloat16, kBiasDecomposed>(a, prm, *dev, mq, mk, mv, mo, stream);
   }
 }
 
