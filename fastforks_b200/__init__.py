@@ -16,12 +16,14 @@ from ._lib import build
 from .attention import attention, check_operands, device_status
 from .errors import BackendUnavailableError, KernelUnavailableError
 from .flash64 import FLASH_VARIANTS, Flash64, check_flash64
+from .host_io import HostAttention
 from .sdpa import scaled_dot_product_attention
 
 __all__ = [
     "FLASH_VARIANTS",
     "BackendUnavailableError",
     "Flash64",
+    "HostAttention",
     "KernelUnavailableError",
     "attention",
     "build",

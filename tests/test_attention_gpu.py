@@ -305,3 +305,42 @@ def test_a_wait_that_runs_out_sets_the_status_word_and_the_context_survives() ->
     q, k, v = qkv.unbind(2)
     got = ff.attention(q, k, v, layout="bnhd")
     assert_close(got.float().cpu().numpy(), oracle_of_packed(qkv, 0.125), unit_scale=True)
+
+
+@pytest.mark.parametrize("depth", [1, 2, 3])
+def test_host_operands_pipeline_matches_the_device_call(depth: int) -> None:
+    """`HostAttention`: five packed tensors in pinned host memory through `depth` staging buffers, twice in a row
+    (staging buffers are reused across calls); every output equals the plain device call bit for bit."""
+    gen = torch.Generator().manual_seed(5)
+    host_qkv = [torch.randn(2, 300, 3, 3, 64, generator=gen).half().pin_memory() for _ in range(5)]
+    host_out = [torch.full((2, 300, 3, 64), float("nan"), dtype=torch.float16).pin_memory() for _ in range(5)]
+    pipe = ff.HostAttention(depth=depth)
+    for _ in range(2):
+        pipe(host_qkv, host_out, 0.125)
+        for x, o in zip(host_qkv, host_out):
+            q, k, v = x.cuda().unbind(2)
+            want = ff.attention(q, k, v, scale=0.125, layout="bnhd")
+            assert torch.equal(o, want.cpu())
+        for o in host_out:
+            o.fill_(float("nan"))
+
+
+def test_repeated_geometry_takes_the_remembered_launch_and_still_checks() -> None:
+    """The second call with the same views goes through the remembered description: same result, new pointers are
+    used, and a call that breaks the contract is still rejected before the launch."""
+    qkv = packed_qkv(2, 197, 4, torch.float16, 1.0, seed=3)
+    q, k, v = qkv.unbind(2)
+    first = ff.attention(q, k, v, layout="bnhd")
+    second = ff.attention(q, k, v, layout="bnhd")
+    assert first.data_ptr() != second.data_ptr() and torch.equal(first, second)
+    other = packed_qkv(2, 197, 4, torch.float16, 1.0, seed=4)
+    third = ff.attention(*other.unbind(2), layout="bnhd")
+    assert_close(third.float().cpu().numpy(), oracle_of_packed(other, 0.125), unit_scale=True, what="remembered launch")
+    with pytest.raises(ValueError, match="requires grad"):
+        ff.attention(q.clone().requires_grad_(), k, v, layout="bnhd")
+    base = torch.zeros(100 * 4 * 64 + 8, device="cuda", dtype=torch.float16)
+    aligned = base[: 100 * 4 * 64].view(1, 100, 4, 64)
+    ff.attention(aligned, aligned, aligned, layout="bnhd")
+    shifted = base[4 : 4 + 100 * 4 * 64].view(1, 100, 4, 64)  # same geometry, 8 bytes off: the library checks
+    with pytest.raises(ValueError, match="16-byte"):
+        ff.attention(shifted, shifted, shifted, layout="bnhd")

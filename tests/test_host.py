@@ -123,3 +123,25 @@ def test_missing_library_fails_loudly(monkeypatch: pytest.MonkeyPatch, tmp_path)
             _lib.library()
     finally:
         _lib.library.cache_clear()
+
+
+def test_host_attention_contract_is_checked_before_any_copy() -> None:
+    """`HostAttention.check` is host logic only: it needs no device and rejects what the copies could not take."""
+    check = ff.HostAttention.check
+    x = torch.zeros(2, 5, 3, 4, 64, dtype=torch.float16)
+    o = torch.zeros(2, 5, 4, 64, dtype=torch.float16)
+    check([], [])
+    with pytest.raises(ValueError, match="outputs"):
+        check([x], [])
+    with pytest.raises(ValueError, match="packed"):
+        check([x[:, :, 0]], [o])
+    with pytest.raises(ValueError, match="expected"):
+        check([x], [o[:, :4].contiguous()])
+    with pytest.raises(ValueError, match="float16"):
+        check([x.float()], [o.float()])
+    with pytest.raises(ValueError, match="contiguous"):
+        check([x.transpose(0, 1).contiguous().transpose(0, 1)], [o])
+    with pytest.raises(ValueError, match="differs"):
+        check([x, torch.zeros(1, 5, 3, 4, 64, dtype=torch.float16)], [o, torch.zeros(1, 5, 4, 64, dtype=torch.float16)])
+    with pytest.raises(ValueError, match="empty"):
+        check([x[:0]], [o[:0]])
