@@ -216,6 +216,64 @@ int device_state(DeviceState** out) {
   return B200_ATTN_OK;
 }
 
+// Cost of a one-tile item in units of a two-tile item of the same head (measured: a lone softmax warpgroup takes
+// 2.8 k clocks per key tile, two interleaved ones 3.6 k for both tiles).
+constexpr double kSingleCost = 0.8;
+
+// Split the query tiles of every (batch, head) into two-tile and one-tile items and deal them to the CTAs so that
+// the most loaded CTA finishes as early as possible. Candidates: every count of two-tile items per head from
+// q_tiles / 2 down; for each, the two-tile items go to the CTAs in consecutive runs of k or k + 1 and the one-tile
+// items fill up the less loaded CTAs first. Fills the split fields of `prm` and returns the grid size.
+unsigned plan_split(AttnParams& prm, long long heads_total, int sms) {
+  const int tiles = prm.q_tiles;
+  double best_span = 0;
+  int best_pairs = -1;
+  struct Plan {
+    int grid, na, ka, kb, a, ea, b, eb;
+  } best{}, cur{};
+  int first = tiles / 2, last = tiles / 2 - 8;
+#ifdef B200_TUNE
+  if (const char* forced = std::getenv("B200_SPLIT_PAIRS")) first = last = std::atoi(forced);  // development builds only
+#endif
+  for (int pairs = first; pairs >= 0 && pairs >= last; --pairs) {
+    const long long P = pairs * heads_total, S = (tiles - 2LL * pairs) * heads_total;
+    const long long grid = P + S < sms ? P + S : sms;
+    cur.grid = static_cast<int>(grid);
+    cur.na = static_cast<int>(P % grid);
+    cur.kb = static_cast<int>(P / grid);
+    cur.ka = cur.kb + 1;
+    if (cur.na == 0) cur.ka = cur.kb;  // no CTA of the first kind
+    // Level the loads with the one-tile items: group A (na CTAs, ka two-tile items), group B (the rest, kb).
+    const long long nb = grid - cur.na;
+    long long a = 0, b = 0, ea = 0, eb = 0, left = S;
+    while (left > 0) {
+      const double level_a = cur.na > 0 ? cur.ka + kSingleCost * a : 1e300;
+      const double level_b = nb > 0 ? cur.kb + kSingleCost * b : 1e300;
+      if (level_b <= level_a) {
+        if (left >= nb) { ++b; left -= nb; } else { eb = left; left = 0; }
+      } else {
+        if (left >= cur.na) { ++a; left -= cur.na; } else { ea = left; left = 0; }
+      }
+    }
+    cur.a = static_cast<int>(a); cur.ea = static_cast<int>(ea); cur.b = static_cast<int>(b); cur.eb = static_cast<int>(eb);
+    double span = 0;
+    if (cur.na > 0) span = std::fmax(span, cur.ka + kSingleCost * (a + (ea > 0 ? 1 : 0)));
+    if (nb > 0) span = std::fmax(span, cur.kb + kSingleCost * (b + (eb > 0 ? 1 : 0)));
+    if (best_pairs < 0 || span < best_span - 1e-9) {
+      best_span = span;
+      best_pairs = pairs;
+      best = cur;
+    }
+  }
+  prm.pairs_per_head = best_pairs;
+  prm.singles_per_head = tiles - 2 * best_pairs;
+  prm.split_na = best.na; prm.split_ka = best.ka; prm.split_kb = best.kb;
+  prm.split_a = best.a; prm.split_ea = best.ea; prm.split_b = best.b; prm.split_eb = best.eb;
+  prm.magic_pairs = div_magic(prm.pairs_per_head);
+  prm.magic_singles = div_magic(prm.singles_per_head);
+  return static_cast<unsigned>(best.grid);
+}
+
 template <typename T, int BIAS>
 int launch(const B200AttnArgs* a, const AttnParams& prm, DeviceState& dev, const CUtensorMap& mq,
            const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, cudaStream_t stream) {
@@ -229,9 +287,9 @@ int launch(const B200AttnArgs* a, const AttnParams& prm, DeviceState& dev, const
     dev.opted_in[form].store(true, std::memory_order_release);
   }
   // Persistent CTAs: one per SM (shared memory and tensor memory allow no more), fewer when there is less work.
-  const long long items = static_cast<long long>(prm.items_per_head) * a->batch * a->heads;
-  const unsigned grid = static_cast<unsigned>(items < dev.sms ? items : dev.sms);
-  kernel<<<grid, kThreads, smem, stream>>>(mq, mk, mv, mo, prm);
+  AttnParams planned = prm;
+  const unsigned grid = plan_split(planned, static_cast<long long>(a->batch) * a->heads, dev.sms);
+  kernel<<<grid, kThreads, smem, stream>>>(mq, mk, mv, mo, planned);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "attention kernel launch");
   return B200_ATTN_OK;
@@ -267,10 +325,8 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
   prm.q_tokens = a->q_tokens;
   prm.kv_tokens = a->kv_tokens;
   prm.q_tiles = (a->q_tokens + kTileRows - 1) / kTileRows;
-  prm.items_per_head = (prm.q_tiles + 1) / 2;
   prm.kv_tiles = (a->kv_tokens + kTileRows - 1) / kTileRows;
   prm.scale_log2 = a->scale * kLog2e;
-  prm.magic_pairs = div_magic(prm.q_tiles / 2);
   prm.magic_heads = div_magic(a->heads);
   prm.o = a->o;
   prm.o_sb = a->o_stride[0];

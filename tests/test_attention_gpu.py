@@ -344,3 +344,15 @@ def test_repeated_geometry_takes_the_remembered_launch_and_still_checks() -> Non
     shifted = base[4 : 4 + 100 * 4 * 64].view(1, 100, 4, 64)  # same geometry, 8 bytes off: the library checks
     with pytest.raises(ValueError, match="16-byte"):
         ff.attention(shifted, shifted, shifted, layout="bnhd")
+
+
+@pytest.mark.parametrize(("b", "n", "h"), [(1, 4096, 12), (2, 1370, 16), (1, 1370, 6), (3, 900, 7), (1, 197, 12), (5, 640, 31)])
+def test_mixed_one_and_two_tile_items_cover_every_query_tile_once(b: int, n: int, h: int) -> None:
+    """Grids smaller than, about equal to and larger than the SM count, where the host splits each head's query
+    tiles into two-tile and one-tile items to level the CTAs' loads: every output row must be written, once, with
+    the right head's result (NaN canary in the output buffer, oracle on the whole tensor)."""
+    qkv = packed_qkv(b, n, h, torch.float16, 1.0, seed=n + b)
+    out = torch.full((b, n, h, 64), float("nan"), dtype=torch.float16, device="cuda")
+    q, k, v = qkv.unbind(2)
+    ff.attention(q, k, v, scale=0.125, layout="bnhd", out=out)
+    assert_close(out.float().cpu().numpy(), oracle_of_packed(qkv, 0.125), unit_scale=True, what=f"[{b},{h},{n},64]")
