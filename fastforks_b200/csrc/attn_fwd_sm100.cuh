@@ -722,6 +722,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
         const int kv0 = j * kTileRows;
         const int kv_valid = min(kTileRows, p.kv_tokens - kv0);
+        float rh0 = 0.f, rh1 = 0.f;  // kBiasDecomposed64: rel_h of the tile's two 64-column halves, natural units
 
         if constexpr (BIAS == kBiasDense) {
           if (p.bias_vec && kv_valid == kTileRows && p.bias.dtype != 2) {
@@ -756,7 +757,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // Keys kv0 .. kv0+127 are (row 2j, all 64 columns) then (row 2j+1, all 64 columns) of the key grid.
           const bool is_half = p.bias2.dtype == 0;
           const int ih = kv0 >> 6;
-          const float rh0 = rh_next0 * kLog2e, rh1 = rh_next1 * kLog2e;
+          // This form keeps the logits in natural units, s * scale + rel_w, one packed FMA per pair of columns: the
+          // factor log2(e) rides on the FMA in front of the exponential, and rel_h, constant over each 64-column
+          // half, is added to that half's maximum and to that FMA's addend instead of to every column.
+          rh0 = rh_next0;
+          rh1 = rh_next1;
           // The next step's pair, in flight behind this whole step.
           rh_next0 = (ih + 2 < p.rel_kh) ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih + 2) : 0.f;
           rh_next1 = (ih + 3 < p.rel_kh) ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih + 3) : 0.f;
@@ -764,14 +769,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // The table's type is decided once per step, not once per word.
           auto add_rel64 = [&](auto half_tag) {
             constexpr bool kHalf = decltype(half_tag)::value;
-            const float2 cc = make_float2(c, c), ll = make_float2(kLog2e, kLog2e);
-            const float2 r0 = make_float2(rh0, rh0), r1 = make_float2(rh1, rh1);
+            const float scale_nat = c * 0.6931471805599453f;  // scale_log2 / log2(e)
+            const float2 cc = make_float2(scale_nat, scale_nat);
 #pragma unroll
             for (int e = 0; e < 32; ++e) {  // one word = rel_w of columns 2e, 2e+1, used by keys 2e.. and 64+2e..
               const float2 rw = unpack2(stage[e], kHalf);
               const int i = 2 * e;
-              const float2 lo = ffma2(make_float2(s[i], s[i + 1]), cc, ffma2(rw, ll, r0));
-              const float2 hi = ffma2(make_float2(s[i + 64], s[i + 65]), cc, ffma2(rw, ll, r1));
+              const float2 lo = ffma2(make_float2(s[i], s[i + 1]), cc, rw);
+              const float2 hi = ffma2(make_float2(s[i + 64], s[i + 65]), cc, rw);
               s[i] = lo.x;
               s[i + 1] = lo.y;
               s[i + 64] = hi.x;
@@ -820,19 +825,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (i >= kv_valid) s[i] = -INFINITY;
         }
 
-        float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
-        float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
+        float m_tile;
+        if constexpr (BIAS == kBiasDecomposed64) {
+          // One maximum per 64-column half (two chains each), rel_h added to each, then to base-2 units.
+          float a0 = max3(s[0], s[1], s[2]), a1 = max3(s[3], s[4], s[5]);
+          float b0 = max3(s[64], s[65], s[66]), b1 = max3(s[67], s[68], s[69]);
 #pragma unroll
-        for (int i = 12; i + 7 < kTileRows; i += 8) {
-          mx0 = max3(mx0, s[i], s[i + 1]);
-          mx1 = max3(mx1, s[i + 2], s[i + 3]);
-          mx2 = max3(mx2, s[i + 4], s[i + 5]);
-          mx3 = max3(mx3, s[i + 6], s[i + 7]);
+          for (int i = 6; i + 3 < 64; i += 4) {
+            a0 = max3(a0, s[i], s[i + 1]);
+            a1 = max3(a1, s[i + 2], s[i + 3]);
+            b0 = max3(b0, s[64 + i], s[65 + i]);
+            b1 = max3(b1, s[66 + i], s[67 + i]);
+          }
+          a0 = max3(a0, s[62], s[63]);  // 6 + 4 * 14 = 62: two columns left per half
+          b0 = max3(b0, s[126], s[127]);
+          m_tile = fmaxf(fmaxf(a0, a1) + rh0, fmaxf(b0, b1) + rh1) * kLog2e;
+        } else {
+          float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
+          float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
+#pragma unroll
+          for (int i = 12; i + 7 < kTileRows; i += 8) {
+            mx0 = max3(mx0, s[i], s[i + 1]);
+            mx1 = max3(mx1, s[i + 2], s[i + 3]);
+            mx2 = max3(mx2, s[i + 4], s[i + 5]);
+            mx3 = max3(mx3, s[i + 6], s[i + 7]);
+          }
+          mx0 = max3(mx0, s[124], s[125]);  // 12 + 8 * 14 = 124: four columns left
+          mx1 = max3(mx1, s[126], s[127]);
+          m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+          if constexpr (BIAS == kBiasNone) m_tile *= c;
         }
-        mx0 = max3(mx0, s[124], s[125]);  // 12 + 8 * 14 = 124: four columns left
-        mx1 = max3(mx1, s[126], s[127]);
-        float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        if constexpr (BIAS == kBiasNone) m_tile *= c;
 
         // Raise the reference maximum only when it pays (or on the first tile).
         const bool raise = m_tile > m_ref + kRescaleThreshold;  // -inf + 8 = -inf: true for any finite first tile
@@ -854,7 +876,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (need_turn) bad |= !mbar_wait_warp_after(turn_early, &sm.turn[t], turn_parity, abort_flag);
         if ((warp & 3) == 0) B200_STAMP(t, step, 2);
         float2 l2a = make_float2(0.f, 0.f), l2b = make_float2(0.f, 0.f);
-        const float2 c2 = (BIAS == kBiasNone) ? make_float2(c, c) : make_float2(1.f, 1.f);
+        const float2 c2 = (BIAS == kBiasNone)           ? make_float2(c, c)
+                          : (BIAS == kBiasDecomposed64) ? make_float2(kLog2e, kLog2e)
+                                                        : make_float2(1.f, 1.f);
         float nm = -m_use;
         uint32_t pk[kTileRows / 2];
         // Midpoint of the section: let the other warpgroup start (the rest of the section reads `nm` through the
@@ -870,7 +894,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // Exponentials of 32 * CHUNKS columns from column 32 * FIRST on.
         auto exp_columns = [&](auto first, auto chunks) {
           constexpr int kFirst = decltype(first)::value * 32, kCount = decltype(chunks)::value * 32;
-          const float2 nm2 = make_float2(nm, nm);
+          float nm_half = nm;
+          if constexpr (BIAS == kBiasDecomposed64) nm_half = fmaf(kFirst < 64 ? rh0 : rh1, kLog2e, nm);  // a section is one half
+          const float2 nm2 = make_float2(nm_half, nm_half);
 #pragma unroll
           for (int i = kFirst; i < kFirst + kCount; i += 4) {
             const float2 xa = ffma2(make_float2(s[i], s[i + 1]), c2, nm2);
