@@ -90,8 +90,10 @@ def check_operands(
         raise ValueError(msg)
 
 
-def _bias_view(name: str, t: torch.Tensor, shape: Sequence[int], q: torch.Tensor) -> torch.Tensor:
-    """`t` as a view broadcast to 4-D `shape` with unit last stride (a copy only if its last stride is not 1)."""
+def _bias_view(name: str, t: torch.Tensor, shape: Sequence[int], q: torch.Tensor) -> tuple[torch.Tensor, bool]:
+    """`t` as a view broadcast to 4-D `shape` with unit last stride, and whether a copy had to be made for it
+    (only if its last stride is not 1 or its last two dims must be materialised)."""
+    source = t
     if t.dtype not in _BIAS_DTYPES or t.device != q.device:
         msg = f"attention: {name} must be float16 / bfloat16 / float32 on {q.device}, got {t.dtype} on {t.device}"
         raise ValueError(msg)
@@ -107,8 +109,9 @@ def _bias_view(name: str, t: torch.Tensor, shape: Sequence[int], q: torch.Tensor
         t = t.expand(t.shape[0], t.shape[1], shape[-2], shape[-1]).contiguous()
     if t.stride(-1) != 1:
         t = t.contiguous()
+    copied = t.untyped_storage().data_ptr() != source.untyped_storage().data_ptr()
     try:
-        return t.expand(*shape)
+        return t.expand(*shape), copied
     except RuntimeError as e:
         msg = f"attention: {name} of shape {tuple(t.shape)} does not broadcast to {tuple(shape)}"
         raise ValueError(msg) from e
@@ -238,12 +241,15 @@ def attention(  # noqa: PLR0913
     a.batch, a.heads, a.q_tokens, a.kv_tokens, a.head_dim = b, h, n, nk, HEAD_DIM
     a.scale = float(HEAD_DIM**-0.5 if scale is None else scale)
     a.schedule = _SCHEDULES[schedule]
-    keep = []  # views that must outlive the launch call
+    keep = []  # tensors made here, which the asynchronous launch still reads after this call returns
     if bias is not None:
+        given_bias_dtype = bias.dtype
         if bias.dtype == torch.bool:  # SDPA: True = takes part in attention
             bias = torch.zeros_like(bias, dtype=q.dtype).masked_fill_(~bias, float("-inf"))
-        bv = _bias_view("bias", bias, (b, h, n, nk), q)
-        keep.append(bv)
+        made = bias.dtype != given_bias_dtype
+        bv, copied = _bias_view("bias", bias, (b, h, n, nk), q)
+        if made or copied:
+            keep.append(bv)
         a.bias, a.bias_dtype = bv.data_ptr(), _BIAS_DTYPES[bv.dtype]
         a.bias_stride[:] = bv.stride()[:3]
     if rel is not None:
@@ -255,9 +261,9 @@ def attention(  # noqa: PLR0913
         if kh * kw != nk:
             msg = f"attention: rel_h / rel_w widths {kh} * {kw} must equal the number of keys {nk}"
             raise ValueError(msg)
-        rh = _bias_view("rel_h", rel_h, (b, h, n, kh), q)
-        rw = _bias_view("rel_w", rel_w, (b, h, n, kw), q)
-        keep += [rh, rw]
+        rh, copied_h = _bias_view("rel_h", rel_h, (b, h, n, kh), q)
+        rw, copied_w = _bias_view("rel_w", rel_w, (b, h, n, kw), q)
+        keep += [t for t, copied in ((rh, copied_h), (rw, copied_w)) if copied]
         a.rel_h, a.rel_w, a.rel_dtype, a.rel_kh, a.rel_kw = rh.data_ptr(), rw.data_ptr(), _BIAS_DTYPES[rh.dtype], kh, kw
         a.rel_h_stride[:] = rh.stride()[:3]
         a.rel_w_stride[:] = rw.stride()[:3]

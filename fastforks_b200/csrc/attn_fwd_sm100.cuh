@@ -223,6 +223,38 @@ __device__ __forceinline__ float load_bias_elem(const void* base, int dtype, int
   return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(base) + idx));
 }
 
+// The same with the table's type known at compile time, and the dispatch that makes it so. A run of loads must sit
+// in ONE arm of the type decision: with the decision inside every load (load_bias_elem in a loop) each load sits
+// behind its own branches, the compiler does not move the loads across them, and their latencies add up instead of
+// overlapping (measured on SAM's 14 x 14 windows: 28 loads per row and item, 7 us per item).
+template <int DT>
+__device__ __forceinline__ float load_bias_elem_t(const void* base, int64_t idx) {
+  if constexpr (DT == 2) return __ldg(reinterpret_cast<const float*>(base) + idx);
+  else if constexpr (DT == 0) return __half2float(__ldg(reinterpret_cast<const __half*>(base) + idx));
+  else return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(base) + idx));
+}
+
+template <typename F>
+__device__ __forceinline__ void for_bias_dtype(int dtype, F&& f) {
+  if (dtype == 2) f(std::integral_constant<int, 2>{});
+  else if (dtype == 0) f(std::integral_constant<int, 0>{});
+  else f(std::integral_constant<int, 1>{});
+}
+
+// The same element as raw bits, and the conversion of such bits: a value fetched a step ahead must stay unconverted
+// until it is used, or the conversion waits for the load where it was issued (measured on SAM's global layers: two
+// converted scalars per key tile cost 32 us of 157).
+__device__ __forceinline__ uint32_t load_bias_bits(const void* base, int dtype, int64_t idx) {
+  if (dtype == 2) return __ldg(reinterpret_cast<const uint32_t*>(base) + idx);
+  return __ldg(reinterpret_cast<const uint16_t*>(base) + idx);
+}
+
+__device__ __forceinline__ float bias_bits_to_float(uint32_t bits, int dtype) {
+  if (dtype == 2) return __uint_as_float(bits);
+  if (dtype == 0) return __half2float(__ushort_as_half(static_cast<unsigned short>(bits)));
+  return __uint_as_float(bits << 16);
+}
+
 // n / d for the divisors the host knows at launch: magic = ceil(2^64 / d) (0 stands for d == 1), exact for every
 // n * d < 2^64. An integer division in device code takes its reciprocal from the MUFU unit, which the softmax warps
 // keep saturated; the multiply does not.
@@ -633,7 +665,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       float l_sum = 0.f;
 
       int64_t bias_row = 0, bias2_row = 0;
-      float rh_next0 = 0.f, rh_next1 = 0.f;             // kBiasDecomposed64: the coming step's two rel_h values
+      uint32_t rh_next0 = 0, rh_next1 = 0;              // kBiasDecomposed64: the coming step's two rel_h values, raw bits
       if constexpr (BIAS != kBiasNone) {
         const int qr = row_valid ? q_row : 0;
         bias_row = b * p.bias.sb + h * p.bias.sh + qr * p.bias.sn;
@@ -642,14 +674,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if constexpr (BIAS == kBiasDecomposed14) {
           // This thread's rows, read back by this thread only: no synchronisation needed.
           float* stage = sm.rel_stage[t][row_in_tile];
-          float tmp[28];
+          for_bias_dtype(p.bias.dtype, [&](auto dt) {  // rel_h and rel_w are of one type
+            constexpr int kDt = decltype(dt)::value;
+            float tmp[28];
 #pragma unroll
-          for (int i = 0; i < 14; ++i) {  // all loads in flight together
-            tmp[i] = load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + i);
-            tmp[14 + i] = load_bias_elem(p.bias2.ptr, p.bias2.dtype, bias2_row + i);
-          }
+            for (int i = 0; i < 14; ++i) {  // all loads in flight together
+              tmp[i] = load_bias_elem_t<kDt>(p.bias.ptr, bias_row + i);
+              tmp[14 + i] = load_bias_elem_t<kDt>(p.bias2.ptr, bias2_row + i);
+            }
 #pragma unroll
-          for (int i = 0; i < 28; ++i) stage[i] = tmp[i] * kLog2e;
+            for (int i = 0; i < 28; ++i) stage[i] = tmp[i] * kLog2e;
+          });
         }
         if constexpr (BIAS == kBiasDecomposed64) {
           // The row's 64 rel_w values (32 words of 16-bit pairs) are the same for every key tile: they are staged
@@ -660,8 +695,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           uint4 v[8];
 #pragma unroll
           for (int u = 0; u < 8; ++u) v[u] = __ldg(src + u);
-          rh_next0 = load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row);
-          rh_next1 = p.rel_kh > 1 ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + 1) : 0.f;
+          rh_next0 = load_bias_bits(p.bias.ptr, p.bias.dtype, bias_row);
+          rh_next1 = p.rel_kh > 1 ? load_bias_bits(p.bias.ptr, p.bias.dtype, bias_row + 1) : 0u;
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             stage[u * 4 + 0] = v[u].x;
@@ -673,17 +708,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if constexpr (BIAS == kBiasDecomposed) {
           if (p.rel_staged) {  // this thread's rows, read back by this thread only: no synchronisation needed
             float* stage = sm.rel_stage[t][row_in_tile];
-            float tmp[kRelStageWords - 1];
+            for_bias_dtype(p.bias.dtype, [&](auto dt) {  // rel_h and rel_w are of one type
+              constexpr int kDt = decltype(dt)::value;
+              float tmp[kRelStageWords - 1];
 #pragma unroll
-            for (int i = 0; i < kRelStageWords - 1; ++i) {  // all loads in flight together
-              const bool in_h = i < p.rel_kh;
-              const bool in_w = !in_h && i < p.rel_kh + p.rel_kw;
-              tmp[i] = in_h   ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + i)
-                       : in_w ? load_bias_elem(p.bias2.ptr, p.bias2.dtype, bias2_row + (i - p.rel_kh))
-                              : 0.f;
-            }
+              for (int i = 0; i < kRelStageWords - 1; ++i) {  // all loads in flight together
+                const bool in_h = i < p.rel_kh;
+                const bool in_w = !in_h && i < p.rel_kh + p.rel_kw;
+                tmp[i] = in_h   ? load_bias_elem_t<kDt>(p.bias.ptr, bias_row + i)
+                         : in_w ? load_bias_elem_t<kDt>(p.bias2.ptr, bias2_row + (i - p.rel_kh))
+                                : 0.f;
+              }
 #pragma unroll
-            for (int i = 0; i < kRelStageWords - 1; ++i) stage[i] = tmp[i] * kLog2e;
+              for (int i = 0; i < kRelStageWords - 1; ++i) stage[i] = tmp[i] * kLog2e;
+            });
           }
         }
       }
@@ -747,11 +785,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               }
             }
           } else {
+            for_bias_dtype(p.bias.dtype, [&](auto dt) {
+              constexpr int kDt = decltype(dt)::value;
 #pragma unroll
-            for (int i = 0; i < kTileRows; ++i) {
-              const float bv = (i < kv_valid) ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + kv0 + i) : 0.f;
-              s[i] = fmaf(s[i], c, bv * kLog2e);
-            }
+              for (int i = 0; i < kTileRows; ++i) {
+                const float bv = (i < kv_valid) ? load_bias_elem_t<kDt>(p.bias.ptr, bias_row + kv0 + i) : 0.f;
+                s[i] = fmaf(s[i], c, bv * kLog2e);
+              }
+            });
           }
         } else if constexpr (BIAS == kBiasDecomposed64) {
           // Keys kv0 .. kv0+127 are (row 2j, all 64 columns) then (row 2j+1, all 64 columns) of the key grid.
@@ -760,11 +801,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // This form keeps the logits in natural units, s * scale + rel_w, one packed FMA per pair of columns: the
           // factor log2(e) rides on the FMA in front of the exponential, and rel_h, constant over each 64-column
           // half, is added to that half's maximum and to that FMA's addend instead of to every column.
-          rh0 = rh_next0;
-          rh1 = rh_next1;
+          rh0 = bias_bits_to_float(rh_next0, p.bias.dtype);
+          rh1 = bias_bits_to_float(rh_next1, p.bias.dtype);
           // The next step's pair, in flight behind this whole step.
-          rh_next0 = (ih + 2 < p.rel_kh) ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih + 2) : 0.f;
-          rh_next1 = (ih + 3 < p.rel_kh) ? load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih + 3) : 0.f;
+          rh_next0 = (ih + 2 < p.rel_kh) ? load_bias_bits(p.bias.ptr, p.bias.dtype, bias_row + ih + 2) : 0u;
+          rh_next1 = (ih + 3 < p.rel_kh) ? load_bias_bits(p.bias.ptr, p.bias.dtype, bias_row + ih + 3) : 0u;
           const uint32_t* stage = reinterpret_cast<const uint32_t*>(sm.rel_stage[t][row_in_tile]);
           // The table's type is decided once per step, not once per word.
           auto add_rel64 = [&](auto half_tag) {
@@ -805,18 +846,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               }
             }
           } else {
-            float bh_val = load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih);
+            for_bias_dtype(p.bias.dtype, [&](auto dt) {  // rel_h and rel_w are of one type
+              constexpr int kDt = decltype(dt)::value;
+              float bh_val = load_bias_elem_t<kDt>(p.bias.ptr, bias_row + ih);
 #pragma unroll
-            for (int i = 0; i < kTileRows; ++i) {
-              float bv = 0.f;
-              if (i < kv_valid) bv = bh_val + load_bias_elem(p.bias2.ptr, p.bias2.dtype, bias2_row + iw);
-              s[i] = fmaf(s[i], c, bv * kLog2e);
-              if (++iw == p.rel_kw) {
-                iw = 0;
-                ++ih;
-                if (i + 1 < kv_valid) bh_val = load_bias_elem(p.bias.ptr, p.bias.dtype, bias_row + ih);
+              for (int i = 0; i < kTileRows; ++i) {
+                float bv = 0.f;
+                if (i < kv_valid) bv = bh_val + load_bias_elem_t<kDt>(p.bias2.ptr, bias2_row + iw);
+                s[i] = fmaf(s[i], c, bv * kLog2e);
+                if (++iw == p.rel_kw) {
+                  iw = 0;
+                  ++ih;
+                  if (i + 1 < kv_valid) bh_val = load_bias_elem_t<kDt>(p.bias.ptr, bias_row + ih);
+                }
               }
-            }
+            });
           }
         }
         if (kv_valid < kTileRows) {

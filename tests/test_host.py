@@ -92,9 +92,11 @@ def test_strides_and_sizes_of_both_layouts() -> None:
 def test_bias_view_broadcasts_without_copy() -> None:
     q = torch.zeros(2, 3, 5, 64, dtype=torch.float16)
     bias = torch.zeros(1, 3, 5, 7, dtype=torch.float16)
-    view = attn_mod._bias_view("bias", bias, (2, 3, 5, 7), q)  # noqa: SLF001
+    view, copied = attn_mod._bias_view("bias", bias, (2, 3, 5, 7), q)  # noqa: SLF001
     assert view.stride() == (0, 35, 7, 1)
-    assert view.data_ptr() == bias.data_ptr()
+    assert view.data_ptr() == bias.data_ptr() and not copied
+    view, copied = attn_mod._bias_view("bias", bias.transpose(2, 3).contiguous().transpose(2, 3), (2, 3, 5, 7), q)  # noqa: SLF001
+    assert copied and view.stride(-1) == 1  # a last stride other than 1 is the one case that needs a copy
     with pytest.raises(ValueError, match="broadcast"):
         attn_mod._bias_view("bias", torch.zeros(4, 3, 5, 7, dtype=torch.float16), (2, 3, 5, 7), q)  # noqa: SLF001
     with pytest.raises(ValueError, match="float16"):
