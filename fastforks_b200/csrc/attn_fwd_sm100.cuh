@@ -72,7 +72,7 @@ enum : uint32_t { kStatusLoader = 1, kStatusMma = 2, kStatusSoftmax = 4, kStatus
 #endif
 // Bias forms. kBiasDecomposed14 is the decomposed form specialised for a 14 x 14 key grid (SAM's windows): both
 // tables of a row sit in registers and every column's pair of indices is a compile-time constant.
-// kBiasDecomposed64 is the decomposed form specialised for rel_kw == 64 with 16-bit, 16-byte aligned
+// kBiasDecomposed64 is the decomposed form specialised for rel_kw == 64, rel_kh a multiple of 8, with 16-bit, 16-byte aligned
 // rel_w rows (SAM's global layers): a key tile then spans exactly two rel_h entries and the whole rel_w row twice.
 enum : int { kBiasNone = 0, kBiasDense = 1, kBiasDecomposed = 2, kBiasDecomposed64 = 3, kBiasDecomposed14 = 4 };
 constexpr int kRelStageWords = 33;  // per-row staging of rel_h | rel_w in shared memory: up to 32 values, odd stride
@@ -239,20 +239,6 @@ __device__ __forceinline__ void for_bias_dtype(int dtype, F&& f) {
   if (dtype == 2) f(std::integral_constant<int, 2>{});
   else if (dtype == 0) f(std::integral_constant<int, 0>{});
   else f(std::integral_constant<int, 1>{});
-}
-
-// The same element as raw bits, and the conversion of such bits: a value fetched a step ahead must stay unconverted
-// until it is used, or the conversion waits for the load where it was issued (measured on SAM's global layers: two
-// converted scalars per key tile cost 32 us of 157).
-__device__ __forceinline__ uint32_t load_bias_bits(const void* base, int dtype, int64_t idx) {
-  if (dtype == 2) return __ldg(reinterpret_cast<const uint32_t*>(base) + idx);
-  return __ldg(reinterpret_cast<const uint16_t*>(base) + idx);
-}
-
-__device__ __forceinline__ float bias_bits_to_float(uint32_t bits, int dtype) {
-  if (dtype == 2) return __uint_as_float(bits);
-  if (dtype == 0) return __half2float(__ushort_as_half(static_cast<unsigned short>(bits)));
-  return __uint_as_float(bits << 16);
 }
 
 // n / d for the divisors the host knows at launch: magic = ceil(2^64 / d) (0 stands for d == 1), exact for every
@@ -665,7 +651,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       float l_sum = 0.f;
 
       int64_t bias_row = 0, bias2_row = 0;
-      uint32_t rh_next0 = 0, rh_next1 = 0;              // kBiasDecomposed64: the coming step's two rel_h values, raw bits
+      // kBiasDecomposed64: rel_h of this row as raw 16-byte groups of eight values, each good for four key tiles
+      // (a tile spans two rows of the key grid); the next group is fetched four tiles ahead and never converted
+      // before it is used. One load per four tiles: every global load in the step costs, two per tile were 20 us of 144.
+      uint4 rh_cur = make_uint4(0, 0, 0, 0), rh_nxt = make_uint4(0, 0, 0, 0);
       if constexpr (BIAS != kBiasNone) {
         const int qr = row_valid ? q_row : 0;
         bias_row = b * p.bias.sb + h * p.bias.sh + qr * p.bias.sn;
@@ -695,8 +684,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           uint4 v[8];
 #pragma unroll
           for (int u = 0; u < 8; ++u) v[u] = __ldg(src + u);
-          rh_next0 = load_bias_bits(p.bias.ptr, p.bias.dtype, bias_row);
-          rh_next1 = p.rel_kh > 1 ? load_bias_bits(p.bias.ptr, p.bias.dtype, bias_row + 1) : 0u;
+          rh_cur = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias.ptr) + bias_row));
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             stage[u * 4 + 0] = v[u].x;
@@ -797,15 +785,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         } else if constexpr (BIAS == kBiasDecomposed64) {
           // Keys kv0 .. kv0+127 are (row 2j, all 64 columns) then (row 2j+1, all 64 columns) of the key grid.
           const bool is_half = p.bias2.dtype == 0;
-          const int ih = kv0 >> 6;
           // This form keeps the logits in natural units, s * scale + rel_w, one packed FMA per pair of columns: the
           // factor log2(e) rides on the FMA in front of the exponential, and rel_h, constant over each 64-column
           // half, is added to that half's maximum and to that FMA's addend instead of to every column.
-          rh0 = bias_bits_to_float(rh_next0, p.bias.dtype);
-          rh1 = bias_bits_to_float(rh_next1, p.bias.dtype);
-          // The next step's pair, in flight behind this whole step.
-          rh_next0 = (ih + 2 < p.rel_kh) ? load_bias_bits(p.bias.ptr, p.bias.dtype, bias_row + ih + 2) : 0u;
-          rh_next1 = (ih + 3 < p.rel_kh) ? load_bias_bits(p.bias.ptr, p.bias.dtype, bias_row + ih + 3) : 0u;
+          const int jj = j & 3;
+          if (jj == 0) {
+            if (j > 0) rh_cur = rh_nxt;
+            if (2 * (j + 4) < p.rel_kh)  // rel_kh is a multiple of 8 in this form: the group is inside the row
+              rh_nxt = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias.ptr) + bias_row) + (j >> 2) + 1);
+          }
+          const uint32_t rh_word = jj == 0 ? rh_cur.x : jj == 1 ? rh_cur.y : jj == 2 ? rh_cur.z : rh_cur.w;
+          const float2 rh01 = unpack2(rh_word, is_half);
+          rh0 = rh01.x;
+          rh1 = rh01.y;
           const uint32_t* stage = reinterpret_cast<const uint32_t*>(sm.rel_stage[t][row_in_tile]);
           // The table's type is decided once per step, not once per word.
           auto add_rel64 = [&](auto half_tag) {

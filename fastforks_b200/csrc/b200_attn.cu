@@ -347,8 +347,12 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
     prm.rel_kw = a->rel_kw;
     prm.magic_rel_kw = div_magic(a->rel_kw);
     prm.rel_staged = a->rel_kh + a->rel_kw <= kRelStageWords - 1;
-    if (a->rel_kw == 64 && a->rel_dtype != B200_ATTN_F32 && aligned16(a->rel_w) && a->rel_w_stride[0] % 8 == 0 &&
-        a->rel_w_stride[1] % 8 == 0 && a->rel_w_stride[2] % 8 == 0)
+    // The 64-wide form reads both tables with 16-byte loads: aligned rows, and rel_h in whole groups of eight.
+    const auto rows16 = [](const void* ptr, const int64_t s[3]) {
+      return aligned16(ptr) && s[0] % 8 == 0 && s[1] % 8 == 0 && s[2] % 8 == 0;
+    };
+    if (a->rel_kw == 64 && a->rel_kh % 8 == 0 && a->rel_dtype != B200_ATTN_F32 && rows16(a->rel_w, a->rel_w_stride) &&
+        rows16(a->rel_h, a->rel_h_stride))
       bias_mode = kBiasDecomposed64;
     else if (a->rel_kh == 14 && a->rel_kw == 14)
       bias_mode = kBiasDecomposed14;

@@ -189,7 +189,8 @@ def test_decomposed_bias_sam_shapes(hw: tuple[int, int], b: int, h: int) -> None
 @pytest.mark.parametrize(
     ("hw", "nq", "dtype", "rel_dtype"),
     [((14, 14), 77, "fp16", torch.float32), ((14, 14), 300, "bf16", torch.bfloat16), ((64, 64), 130, "bf16", torch.bfloat16),
-     ((3, 64), 200, "fp16", torch.float16), ((1, 64), 64, "fp16", torch.float16)],
+     ((3, 64), 200, "fp16", torch.float16), ((1, 64), 64, "fp16", torch.float16),
+     ((8, 64), 300, "bf16", torch.bfloat16), ((16, 64), 130, "fp16", torch.float16), ((24, 64), 257, "fp16", torch.bfloat16)],
 )
 def test_decomposed_bias_fast_paths_cross_length(hw: tuple[int, int], nq: int, dtype: str, rel_dtype: torch.dtype) -> None:
     """The 14 x 14 and 64-wide forms of the decomposed bias with a query count that differs from the key count
