@@ -125,22 +125,23 @@ _PREPARED = threading.local()
 _PREPARED_LIMIT = 256
 
 
-def _geometry_key(q, k, v, layout, out, schedule):  # noqa: ANN001, ANN202
+def _geometry_key(q, k, v, layout, out, schedule, rel=None):  # noqa: ANN001, ANN202, PLR0913
     return (
         q.dtype, k.dtype, v.dtype, q.device, k.device, v.device, layout, schedule, q.shape, k.shape, v.shape,
         q.stride(), k.stride(), v.stride(),
         None if out is None else (out.dtype, out.device, out.shape, out.stride()),
+        None if rel is None else tuple((t.dtype, t.device, t.shape, t.stride()) for t in rel),
     )  # fmt: skip
 
 
-def _launch_prepared(q, k, v, scale, layout, out, schedule):  # noqa: ANN001, ANN202, PLR0913
+def _launch_prepared(q, k, v, scale, layout, out, schedule, rel=None):  # noqa: ANN001, ANN202, PLR0913
     """Launch from a remembered description of this geometry; None when there is none (the full path then runs)."""
     table = getattr(_PREPARED, "table", None)
     if table is None:
         return None
     try:
-        entry = table.get(_geometry_key(q, k, v, layout, out, schedule))
-    except (AttributeError, TypeError):  # not tensors: let the full path raise its ValueError
+        entry = table.get(_geometry_key(q, k, v, layout, out, schedule, rel))
+    except (AttributeError, TypeError, ValueError):  # not tensors: let the full path raise its ValueError
         return None
     if entry is None:
         return None
@@ -153,6 +154,8 @@ def _launch_prepared(q, k, v, scale, layout, out, schedule):  # noqa: ANN001, AN
         o = torch.empty(o_shape, device=q.device, dtype=q.dtype)
         out = o.transpose(1, 2) if layout == "bhnd" else o
     a.q, a.k, a.v, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    if rel is not None:  # remembered only where the tables went in as they are (broadcast views of the same memory)
+        a.rel_h, a.rel_w = rel[0].data_ptr(), rel[1].data_ptr()
     a.scale = float(HEAD_DIM**-0.5 if scale is None else scale)
     code = _lib.library().b200_attn_fwd(ctypes.byref(a), torch._C._cuda_getCurrentRawStream(index))  # noqa: SLF001
     if code != _lib.OK:
@@ -160,7 +163,7 @@ def _launch_prepared(q, k, v, scale, layout, out, schedule):  # noqa: ANN001, AN
     return out
 
 
-def _remember(a, q, k, v, out, layout, schedule) -> None:  # noqa: ANN001, PLR0913
+def _remember(a, q, k, v, out, layout, schedule, rel=None) -> None:  # noqa: ANN001, PLR0913
     """Keep the checked description `a` of this geometry for the calling thread (`out` as the caller gave it)."""
     index = q.device.index
     if index is None or index != torch.cuda.current_device():
@@ -171,7 +174,7 @@ def _remember(a, q, k, v, out, layout, schedule) -> None:  # noqa: ANN001, PLR09
     if len(table) >= _PREPARED_LIMIT:
         table.clear()
     copy = _lib.B200AttnArgs.from_buffer_copy(a)
-    table[_geometry_key(q, k, v, layout, out, schedule)] = (copy, (a.batch, a.q_tokens, a.heads, HEAD_DIM), index)
+    table[_geometry_key(q, k, v, layout, out, schedule, rel)] = (copy, (a.batch, a.q_tokens, a.heads, HEAD_DIM), index)
 
 
 def attention(  # noqa: PLR0913
@@ -211,8 +214,8 @@ def attention(  # noqa: PLR0913
         KernelUnavailableError: The CUDA library is not built or does not load.
         RuntimeError: A CUDA error at launch.
     """
-    if bias is None and rel is None:
-        done = _launch_prepared(q, k, v, scale, layout, out, schedule)
+    if bias is None:
+        done = _launch_prepared(q, k, v, scale, layout, out, schedule, rel)
         if done is not None:
             return done
     check_operands(q, k, v, layout, out)
@@ -268,8 +271,8 @@ def attention(  # noqa: PLR0913
         a.rel_h_stride[:] = rh.stride()[:3]
         a.rel_w_stride[:] = rw.stride()[:3]
 
-    if bias is None and rel is None:
-        _remember(a, q, k, v, given_out, layout, schedule)
+    if bias is None and not keep:  # no temporaries: the same geometry can be launched from the caller's pointers alone
+        _remember(a, q, k, v, given_out, layout, schedule, rel)
     index = q.device.index if q.device.index is not None else torch.cuda.current_device()
     if index != torch.cuda.current_device():
         with torch.cuda.device(index):
