@@ -387,6 +387,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  // The launch allows this grid to start while the kernel before it in the stream is still draining (programmatic
+  // stream serialisation): the set-up above touches no global memory and overlaps that kernel's tail; everything
+  // below reads or writes global memory and waits here until the earlier kernel has completed and its writes are
+  // visible. Without an earlier kernel, or without the launch attribute, the wait returns at once.
+  grid_dependency_wait();
   const uint32_t tmem = sm.tmem_base;
   volatile uint32_t* abort_flag = &sm.abort;
   const CtaWork& cw = sm.work;

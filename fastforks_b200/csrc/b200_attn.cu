@@ -289,8 +289,22 @@ int launch(const B200AttnArgs* a, const AttnParams& prm, DeviceState& dev, const
   // Persistent CTAs: one per SM (shared memory and tensor memory allow no more), fewer when there is less work.
   AttnParams planned = prm;
   const unsigned grid = plan_split(planned, static_cast<long long>(a->batch) * a->heads, dev.sms);
-  kernel<<<grid, kThreads, smem, stream>>>(mq, mk, mv, mo, planned);
-  cudaError_t e = cudaGetLastError();
+  // Programmatic stream serialisation: the CTAs of this grid may be scheduled while the previous kernel of the stream
+  // drains; the kernel waits for that kernel's completion itself (grid_dependency_wait) before it touches global
+  // memory, so its set-up (barriers, tensor memory, descriptor prefetch) and the launch latency hide behind the
+  // predecessor's tail.
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&config, kernel, mq, mk, mv, mo, planned);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "attention kernel launch");
   return B200_ATTN_OK;
 }

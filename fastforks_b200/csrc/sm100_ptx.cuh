@@ -166,6 +166,10 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 // TMA (tiled tensor copies through a CUtensorMap). Loads signal an mbarrier with their byte count.
 // x is the innermost coordinate and must keep the copy 16-byte aligned.
 // ---------------------------------------------------------------------------------------------
+// Wait until the grids this one depends on (the kernel launched before it in the stream, when this one was launched
+// with programmatic stream serialisation) have completed and flushed their memory operations.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
