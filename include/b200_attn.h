@@ -102,6 +102,10 @@ typedef struct B200AttnArgs {
  * of the current device and returns without synchronising.  Replaces the `flash64_*` launch
  * (fastbb/__init__.py:130-135) and the SDPA call sites named above.
  * Arguments are checked before anything is launched; a non-zero return means nothing ran.
+ * The kernel is launched with programmatic stream serialisation: its set-up may overlap the tail of the kernel
+ * before it in the stream, and it waits on the device for that kernel's completion before it reads or writes
+ * global memory, so stream order holds for every buffer.  Thread-safe: per-device values are looked up once under
+ * a mutex, nothing else is shared between calls.
  */
 int b200_attn_fwd(const B200AttnArgs* args, void* stream);
 
