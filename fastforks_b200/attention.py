@@ -203,7 +203,8 @@ def attention(  # noqa: PLR0913
             (`src/fastforks/promptable_segmentation/models/sam/net/image_encoder.py:326-362`), never materialised.
         layout: `"bhnd"` or `"bnhd"`.
         out: Optional output view of q's shape and dtype.
-        schedule: `"auto"`, `"long"` or `"short"` tile schedule.
+        schedule: `"auto"`, `"long"` or `"short"` tile schedule; `"auto"` takes the short one for at most 256 keys whose last
+            128-key tile holds at most 96 (e.g. 197 tokens). The result does not depend on it.
 
     Returns:
         A tensor of q's shape. Without `out` its memory is `[B, N, heads, 64]`-contiguous in both layouts, so the

@@ -328,7 +328,7 @@ __device__ __forceinline__ WorkItem decode_item(const AttnParams& p, const CtaWo
 // Persistent kernel: every CTA works through its own list of items (cta_work). All barrier phases and ring
 // positions are running counters, so the loader prefetches the next item's Q / K / V while the current one is
 // still being computed and tensor memory and barriers are set up once per CTA.
-template <typename T, int BIAS>
+template <typename T, int BIAS, bool SHORT>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const AttnParams p) {
@@ -953,7 +953,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         using std::integral_constant;
         exp_columns(integral_constant<int, 0>{}, integral_constant<int, 2>{});
         midpoint();
-        exp_columns(integral_constant<int, 2>{}, integral_constant<int, 2>{});
+        if constexpr (SHORT) {
+          // Short-sequence schedule. The last 32 columns of a ragged last key tile that hold no key at all (197 keys:
+          // 69 in the second tile) need no exponentials: their logits are -inf and their P is never read (P V stops
+          // at the last key's k-step). One CTA-uniform branch: -6 % on [256,12,197,64]. With eleven key tiles
+          // the branch is taken once in eleven steps and its effect on the step's schedule costs more than it
+          // saves (+4 % on [32,24,1370,64] bf16), hence a schedule of its own.
+          exp_columns(integral_constant<int, 2>{}, integral_constant<int, 1>{});
+          if (kv_valid > 96) {
+            exp_columns(integral_constant<int, 3>{}, integral_constant<int, 1>{});
+          } else {
+#pragma unroll
+            for (int i = 48; i < 64; ++i) pk[i] = 0u;
+          }
+        } else {
+          exp_columns(integral_constant<int, 2>{}, integral_constant<int, 2>{});
+        }
         if ((warp & 3) == 0) B200_STAMP(t, step, 3);
         l_sum += (l2a.x + l2a.y) + (l2b.x + l2b.y);
 

@@ -175,7 +175,11 @@ int validate(const B200AttnArgs* a, int* bias_mode, int* schedule) {
 
   if (a->schedule < B200_ATTN_SCHED_AUTO || a->schedule > B200_ATTN_SCHED_SHORT)
     return fail(B200_ATTN_BAD_CONFIG, "schedule %d unknown", a->schedule);
-  *schedule = B200_ATTN_SCHED_LONG;
+  // Short schedule: at most two key tiles and a last one whose final 32 columns hold no key (its exponentials are skipped).
+  const int kv_tiles = (a->kv_tokens + kTileRows - 1) / kTileRows;
+  const int kv_last = a->kv_tokens - (kv_tiles - 1) * kTileRows;
+  const bool short_pays = kv_tiles <= 2 && kv_last <= kTileRows - 32;
+  *schedule = a->schedule != B200_ATTN_SCHED_AUTO ? a->schedule : short_pays ? B200_ATTN_SCHED_SHORT : B200_ATTN_SCHED_LONG;
   tl_error[0] = '\0';
   return B200_ATTN_OK;
 }
@@ -184,7 +188,7 @@ int validate(const B200AttnArgs* a, int* bias_mode, int* schedule) {
 // status word and which kernels already have their shared-memory opt-in (the opt-in is per device and per kernel).
 // The runtime calls behind these cost more than the rest of the host path of a launch-bound call.
 constexpr int kMaxDevices = 64;
-constexpr int kKernelForms = 10;  // 2 dtypes x 5 bias forms
+constexpr int kKernelForms = 20;  // 2 dtypes x 5 bias forms x 2 schedules
 struct DeviceState {
   std::atomic<bool> ready{false};
   int sms = 0;
@@ -274,12 +278,12 @@ unsigned plan_split(AttnParams& prm, long long heads_total, int sms) {
   return static_cast<unsigned>(best.grid);
 }
 
-template <typename T, int BIAS>
+template <typename T, int BIAS, bool SHORT>
 int launch(const B200AttnArgs* a, const AttnParams& prm, DeviceState& dev, const CUtensorMap& mq,
            const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, cudaStream_t stream) {
-  auto kernel = attn_fwd_kernel<T, BIAS>;
+  auto kernel = attn_fwd_kernel<T, BIAS, SHORT>;
   constexpr int smem = static_cast<int>(sizeof(AttnSmem)) + 1024;
-  constexpr int form = BIAS * 2 + (std::is_same<T, __half>::value ? 0 : 1);
+  constexpr int form = (BIAS * 2 + (std::is_same<T, __half>::value ? 0 : 1)) * 2 + (SHORT ? 1 : 0);
   static_assert(form < kKernelForms, "kernel form index");
   if (!dev.opted_in[form].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -307,6 +311,17 @@ int launch(const B200AttnArgs* a, const AttnParams& prm, DeviceState& dev, const
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "attention kernel launch");
   return B200_ATTN_OK;
+}
+
+// The short schedule exists for every bias form but the 64-wide one (its key counts are multiples of 64, where the
+// long schedule loses nothing worth a second set of kernels).
+template <typename T, int BIAS>
+int launch_sched(bool short_sched, const B200AttnArgs* a, const AttnParams& prm, DeviceState& dev, const CUtensorMap& mq,
+                 const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, cudaStream_t stream) {
+  if constexpr (BIAS != kBiasDecomposed64) {
+    if (short_sched) return launch<T, BIAS, true>(a, prm, dev, mq, mk, mv, mo, stream);
+  }
+  return launch<T, BIAS, false>(a, prm, dev, mq, mk, mv, mo, stream);
 }
 
 }  // namespace
@@ -381,20 +396,20 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
   const bool f16 = a->dtype == B200_ATTN_F16;
   switch (bias_mode) {
     case kBiasNone:
-      return f16 ? launch<__half, kBiasNone>(a, prm, *dev, mq, mk, mv, mo, stream)
-                 : launch<__nv_bfloat16, kBiasNone>(a, prm, *dev, mq, mk, mv, mo, stream);
+      return f16 ? launch_sched<__half, kBiasNone>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream)
+                 : launch_sched<__nv_bfloat16, kBiasNone>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream);
     case kBiasDense:
-      return f16 ? launch<__half, kBiasDense>(a, prm, *dev, mq, mk, mv, mo, stream)
-                 : launch<__nv_bfloat16, kBiasDense>(a, prm, *dev, mq, mk, mv, mo, stream);
+      return f16 ? launch_sched<__half, kBiasDense>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream)
+                 : launch_sched<__nv_bfloat16, kBiasDense>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream);
     case kBiasDecomposed64:
-      return f16 ? launch<__half, kBiasDecomposed64>(a, prm, *dev, mq, mk, mv, mo, stream)
-                 : launch<__nv_bfloat16, kBiasDecomposed64>(a, prm, *dev, mq, mk, mv, mo, stream);
+      return f16 ? launch_sched<__half, kBiasDecomposed64>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream)
+                 : launch_sched<__nv_bfloat16, kBiasDecomposed64>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream);
     case kBiasDecomposed14:
-      return f16 ? launch<__half, kBiasDecomposed14>(a, prm, *dev, mq, mk, mv, mo, stream)
-                 : launch<__nv_bfloat16, kBiasDecomposed14>(a, prm, *dev, mq, mk, mv, mo, stream);
+      return f16 ? launch_sched<__half, kBiasDecomposed14>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream)
+                 : launch_sched<__nv_bfloat16, kBiasDecomposed14>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream);
     default:
-      return f16 ? launch<__half, kBiasDecomposed>(a, prm, *dev, mq, mk, mv, mo, stream)
-                 : launch<__nv_bfloat16, kBiasDecomposed>(a, prm, *dev, mq, mk, mv, mo, stream);
+      return f16 ? launch_sched<__half, kBiasDecomposed>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream)
+                 : launch_sched<__nv_bfloat16, kBiasDecomposed>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream);
   }
 }
 

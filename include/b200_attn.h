@@ -41,9 +41,12 @@ extern "C" {
 #define B200_ATTN_BF16 1
 #define B200_ATTN_F32 2 /* bias tensors only */
 
-/* Tile schedule hints. One persistent schedule serves every sequence length today (one CTA per SM walks work items
- * of one or two 128-row query tiles of one head, the next item's tiles prefetched while the current one computes),
- * so the three values run the same kernel; they are part of the ABI so that a caller's hint keeps its meaning. */
+/* Tile schedule hints. Both schedules are the same persistent kernel (one CTA per SM walks work items of one or two
+ * 128-row query tiles of one head, the next item's tiles prefetched while the current one computes). The short one
+ * skips the exponentials of the last 32 columns of a ragged last key tile when they hold no key at all, which pays
+ * for sequences of at most two key tiles (197 tokens: 69 keys in the second tile) and costs the long sequences a
+ * little. AUTO picks SHORT for at most 256 keys whose last tile holds at most 96, else LONG; b200_attn_query
+ * reports the choice. Results are identical bit for bit. */
 #define B200_ATTN_SCHED_AUTO 0
 #define B200_ATTN_SCHED_LONG 1
 #define B200_ATTN_SCHED_SHORT 2

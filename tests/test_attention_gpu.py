@@ -358,3 +358,17 @@ def test_mixed_one_and_two_tile_items_cover_every_query_tile_once(b: int, n: int
     q, k, v = qkv.unbind(2)
     ff.attention(q, k, v, scale=0.125, layout="bnhd", out=out)
     assert_close(out.float().cpu().numpy(), oracle_of_packed(qkv, 0.125), unit_scale=True, what=f"[{b},{h},{n},64]")
+
+
+@pytest.mark.parametrize("schedule", ["auto", "long", "short"])
+@pytest.mark.parametrize("n", [197, 160, 225, 256, 130, 1370])
+def test_both_schedules_give_the_same_result(schedule: str, n: int) -> None:
+    """The short schedule skips the exponentials of a last key tile's final 32 columns when they hold no key (197,
+    160, 130 keys: taken; 225, 256: tile too full; 1370: only on request). Any hint must give the oracle's result,
+    and the two schedules the same bits."""
+    qkv = packed_qkv(2, n, 3, torch.float16, 1.0, seed=n)
+    q, k, v = qkv.unbind(2)
+    got = ff.attention(q, k, v, scale=0.125, layout="bnhd", schedule=schedule)
+    assert_close(got.float().cpu().numpy(), oracle_of_packed(qkv, 0.125), unit_scale=True, what=f"{schedule} n={n}")
+    other = ff.attention(q, k, v, scale=0.125, layout="bnhd", schedule="long")
+    assert torch.equal(got, other)
