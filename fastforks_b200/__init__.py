@@ -13,7 +13,7 @@ import logging
 
 from . import _lib
 from ._lib import build
-from .attention import attention, check_operands, device_status
+from .attention import attention, check_operands, device_status, reserve_workspace
 from .errors import BackendUnavailableError, KernelUnavailableError
 from .flash64 import FLASH_VARIANTS, Flash64, check_flash64
 from .host_io import HostAttention
@@ -31,6 +31,7 @@ __all__ = [
     "check_operands",
     "device_status",
     "kernels_unavailable_reason",
+    "reserve_workspace",
     "resolve_mode",
     "scaled_dot_product_attention",
     "version",

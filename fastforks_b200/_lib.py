@@ -9,7 +9,9 @@ from __future__ import annotations
 
 import ctypes
 import functools
+import hashlib
 import os
+import re
 import shutil
 import subprocess
 import threading
@@ -35,8 +37,8 @@ NVCC_FLAGS = (
 
 # Every symbol include/b200_attn.h declares.
 EXPORTS = (
-    "b200_attn_fwd", "b200_attn_query", "b200_attn_status", "b200_attn_selftest_wait_limit", "b200_attn_last_error",
-    "b200_attn_version",
+    "b200_attn_fwd", "b200_attn_query", "b200_attn_plan", "b200_attn_workspace_size", "b200_attn_status",
+    "b200_attn_selftest_wait_limit", "b200_attn_last_error", "b200_attn_version",
 )  # fmt: skip
 
 OK, UNSUPPORTED, BAD_CONFIG, CUDA_ERROR_BASE = 0, 1, -1, 1000
@@ -75,16 +77,36 @@ class B200AttnArgs(ctypes.Structure):
         ("rel_h_stride", ctypes.c_int64 * 3),
         ("rel_w_stride", ctypes.c_int64 * 3),
         ("schedule", ctypes.c_int32),
-        ("reserved", ctypes.c_int32),
+        ("test_flags", ctypes.c_int32),
+        ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_int64),
     )
 
 
-def needs_build() -> bool:
-    """True when the shared object is missing or older than one of its sources."""
+def source_hash() -> str:
+    """Digest of the sources the shared object is compiled from (16 hex digits). The build passes it to the compiler,
+    which puts it into the library's version string, so a binary can be matched with the sources beside it."""
+    digest = hashlib.sha256()
+    for path in sorted((SOURCE, *HEADERS), key=lambda f: f.name):
+        digest.update(path.name.encode())
+        digest.update(path.read_bytes())
+    return digest.hexdigest()[:16]
+
+
+_HASH_IN_BINARY = re.compile(rb"b200attn-src:([0-9a-f]{16})")
+
+
+def built_hash() -> str | None:
+    """The source digest compiled into the shared object on disk (read from the file, without loading it), or None."""
     if not SHARED_OBJECT.exists():
-        return True
-    built = SHARED_OBJECT.stat().st_mtime
-    return any(p.exists() and p.stat().st_mtime > built for p in (SOURCE, *HEADERS))
+        return None
+    found = _HASH_IN_BINARY.search(SHARED_OBJECT.read_bytes())
+    return found.group(1).decode() if found else None
+
+
+def needs_build() -> bool:
+    """True when the shared object is missing or was compiled from other sources than the ones beside it."""
+    return built_hash() != source_hash()
 
 
 def build(*, force: bool = False, verbose: bool = False) -> Path:
@@ -99,7 +121,8 @@ def build(*, force: bool = False, verbose: bool = False) -> Path:
     if not Path(nvcc).exists():
         raise KernelUnavailableError(LIBRARY, "nvcc not found: cannot build libb200attn.so")
     tmp = SHARED_OBJECT.with_suffix(f".{os.getpid()}.tmp.so")
-    cmd = [nvcc, *NVCC_FLAGS, *(("-Xptxas", "-v") if verbose else ()), "-o", str(tmp), str(SOURCE)]
+    cmd = [nvcc, *NVCC_FLAGS, f'-DB200_SOURCE_HASH="{source_hash()}"', *(("-Xptxas", "-v") if verbose else ()),
+           "-o", str(tmp), str(SOURCE)]  # fmt: skip
     proc = subprocess.run(cmd, capture_output=True, text=True, check=False)
     if proc.returncode != 0:
         tmp.unlink(missing_ok=True)
@@ -120,10 +143,11 @@ def library() -> ctypes.CDLL:
     Raises:
         KernelUnavailableError: The shared object is not built or does not load (the message says which).
     """
-    if not SHARED_OBJECT.exists():
-        raise KernelUnavailableError(
-            LIBRARY, f"{SHARED_OBJECT.name} is not built; run `python -c 'import fastforks_b200; fastforks_b200.build()'`"
-        )
+    if needs_build():
+        # A binary of other sources must never answer for these, and nothing is built behind the caller's back.
+        state = "is not built" if not SHARED_OBJECT.exists() else "was built from other sources than the ones beside it"
+        how = "run `python -c 'import fastforks_b200; fastforks_b200.build()'`"
+        raise KernelUnavailableError(LIBRARY, f"{SHARED_OBJECT.name} {state}; {how}")
     try:
         lib = ctypes.CDLL(str(SHARED_OBJECT))
     except OSError as e:
@@ -135,6 +159,11 @@ def library() -> ctypes.CDLL:
     lib.b200_attn_fwd.restype = ctypes.c_int
     lib.b200_attn_query.argtypes = (ctypes.POINTER(B200AttnArgs), ctypes.POINTER(ctypes.c_int32))
     lib.b200_attn_query.restype = ctypes.c_int
+    i32p = ctypes.POINTER(ctypes.c_int32)
+    lib.b200_attn_plan.argtypes = (ctypes.POINTER(B200AttnArgs), ctypes.c_int32, ctypes.c_int32, i32p, i32p, ctypes.c_int32, i32p, i32p)
+    lib.b200_attn_plan.restype = ctypes.c_int
+    lib.b200_attn_workspace_size.argtypes = (ctypes.POINTER(ctypes.c_int64),)
+    lib.b200_attn_workspace_size.restype = ctypes.c_int
     lib.b200_attn_status.argtypes = (ctypes.POINTER(ctypes.c_uint32),)
     lib.b200_attn_status.restype = ctypes.c_int
     lib.b200_attn_selftest_wait_limit.argtypes = (ctypes.c_uint32, ctypes.c_void_p)

@@ -117,6 +117,52 @@ def _bias_view(name: str, t: torch.Tensor, shape: Sequence[int], q: torch.Tensor
         raise ValueError(msg) from e
 
 
+# Scratch memory for launches that split long sequences along the keys (include/b200_attn.h: `workspace`), one per
+# (device, stream) like the reference's GEMM workspaces (`_PW_WS`, src/fastforks/_optimize/ops.py:248-296): launches
+# on one stream run one after the other, launches on different streams never share one. Zeroed when allocated; the
+# kernel leaves it ready for the next launch.
+_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+_WORKSPACES_LOCK = threading.Lock()
+
+
+def reserve_workspace(device: torch.device | int | None = None) -> torch.Tensor:
+    """The scratch tensor of the current stream of `device`, allocated and zeroed on first use.
+
+    `attention()` calls this itself. Call it by hand, on the stream a CUDA graph will be captured on, BEFORE the
+    capture: nothing is allocated while a stream is capturing, so a capture without a reserved workspace launches
+    the unsplit form (same result within rounding, slower where the split pays).
+    """
+    index = device if isinstance(device, int) else None if device is None else torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    stream = torch._C._cuda_getCurrentRawStream(index)  # noqa: SLF001
+    ws = _WORKSPACES.get((index, stream))
+    if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None  # type: ignore[return-value]
+        size = ctypes.c_int64(0)
+        with torch.cuda.device(index):
+            _lib.raise_for_code(_lib.library().b200_attn_workspace_size(ctypes.byref(size)), "attention workspace")
+        with _WORKSPACES_LOCK:
+            ws = _WORKSPACES.get((index, stream))
+            if ws is None:
+                ws = _WORKSPACES[(index, stream)] = torch.zeros(size.value, dtype=torch.uint8, device=torch.device("cuda", index))
+    return ws
+
+
+_SPLIT_MIN_KEYS = 257  # the library only ever splits sequences of more than two 128-key tiles
+
+
+def _attach_workspace(a: _lib.B200AttnArgs, index: int) -> None:
+    """Point the launch description at the current stream's workspace (or at none: short sequences, which are
+    never split and are the launch-bound ones, and captures without a reserved workspace)."""
+    ws = reserve_workspace(index) if a.kv_tokens >= _SPLIT_MIN_KEYS else None
+    if ws is None:
+        a.workspace, a.workspace_bytes = None, 0
+    else:
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+
+
 # Launch descriptions already checked once, per thread: geometry key -> (args struct, output shape). A ViT calls the
 # operator with the same views in every block and every forward; for launch-bound shapes (one image of 197 tokens) the
 # checks and the ctypes set-up of a call cost more than the kernel, so a repeated geometry only has its four
@@ -157,6 +203,7 @@ def _launch_prepared(q, k, v, scale, layout, out, schedule, rel=None):  # noqa: 
     if rel is not None:  # remembered only where the tables went in as they are (broadcast views of the same memory)
         a.rel_h, a.rel_w = rel[0].data_ptr(), rel[1].data_ptr()
     a.scale = float(HEAD_DIM**-0.5 if scale is None else scale)
+    _attach_workspace(a, index)
     code = _lib.library().b200_attn_fwd(ctypes.byref(a), torch._C._cuda_getCurrentRawStream(index))  # noqa: SLF001
     if code != _lib.OK:
         _lib.raise_for_code(code, "attention")
@@ -188,6 +235,7 @@ def attention(  # noqa: PLR0913
     layout: str = "bhnd",
     out: torch.Tensor | None = None,
     schedule: str = "auto",
+    _general_merge: bool = False,
 ) -> torch.Tensor:
     """`softmax(scale * q k^T + bias) v` on the B200 kernels; q, k, v are views, nothing is copied.
 
@@ -215,7 +263,7 @@ def attention(  # noqa: PLR0913
         KernelUnavailableError: The CUDA library is not built or does not load.
         RuntimeError: A CUDA error at launch.
     """
-    if bias is None:
+    if bias is None and not _general_merge:
         done = _launch_prepared(q, k, v, scale, layout, out, schedule, rel)
         if done is not None:
             return done
@@ -245,6 +293,7 @@ def attention(  # noqa: PLR0913
     a.batch, a.heads, a.q_tokens, a.kv_tokens, a.head_dim = b, h, n, nk, HEAD_DIM
     a.scale = float(HEAD_DIM**-0.5 if scale is None else scale)
     a.schedule = _SCHEDULES[schedule]
+    a.test_flags = 1 if _general_merge else 0  # tests only: every merge of a split launch takes its general route
     keep = []  # tensors made here, which the asynchronous launch still reads after this call returns
     if bias is not None:
         given_bias_dtype = bias.dtype
@@ -272,13 +321,15 @@ def attention(  # noqa: PLR0913
         a.rel_h_stride[:] = rh.stride()[:3]
         a.rel_w_stride[:] = rw.stride()[:3]
 
-    if bias is None and not keep:  # no temporaries: the same geometry can be launched from the caller's pointers alone
+    if bias is None and not keep and not _general_merge:  # no temporaries: the same geometry can be launched from the caller's pointers alone
         _remember(a, q, k, v, given_out, layout, schedule, rel)
     index = q.device.index if q.device.index is not None else torch.cuda.current_device()
     if index != torch.cuda.current_device():
         with torch.cuda.device(index):
+            _attach_workspace(a, index)
             code = lib.b200_attn_fwd(ctypes.byref(a), torch._C._cuda_getCurrentRawStream(index))  # noqa: SLF001
     else:
+        _attach_workspace(a, index)
         code = lib.b200_attn_fwd(ctypes.byref(a), torch._C._cuda_getCurrentRawStream(index))  # noqa: SLF001
     _lib.raise_for_code(code, "attention")
     for t in keep:  # the launch is asynchronous: tie temporaries to the stream
@@ -294,5 +345,10 @@ def device_status(device: torch.device | int | None = None) -> int:
     word = ctypes.c_uint32(0)
     with torch.cuda.device(device):
         code = _lib.library().b200_attn_status(ctypes.byref(word))
+        index = torch.cuda.current_device()
     _lib.raise_for_code(code, "attention status")
+    if word.value != 0:  # a launch that gave up may have left flags raised in a workspace: start them from zero again
+        for (dev, _), ws in list(_WORKSPACES.items()):
+            if dev == index:
+                ws.zero_()
     return int(word.value)

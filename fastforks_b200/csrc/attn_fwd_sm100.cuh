@@ -52,6 +52,34 @@ constexpr float kRescaleThreshold = 8.0f;             // log2 units: P stays bel
 
 enum : uint32_t { kStatusLoader = 1, kStatusMma = 2, kStatusSoftmax = 4, kStatusStore = 16 };  // 8: the wait self-test
 
+// Key-split mode: the key-tile steps of all items form one line (two-tile items first, head by head, then the
+// one-tile items) and every CTA takes one contiguous run of it, cut so that the runs cost the same. A step of a
+// two-tile item costs kPairCost units, a step of a one-tile item kSingleCost (a lone softmax warpgroup takes 0.78 of
+// the time two interleaved ones take for both tiles).
+constexpr int kPairCost = 64, kSingleCost = 50;
+// An item that is cut has one part per CTA of a run of consecutive CTAs. A part's result is, per query tile, its
+// unnormalised output as [16 column groups][128 rows] of float4 (consecutive threads, consecutive addresses), the
+// rows' reference maxima and their row sums. How the parts meet:
+//   * the part with the item's first keys ("owner") is its CTA's LAST item, every later part its CTA's FIRST item,
+//     so as a rule the later parts are complete long before the owner is;
+//   * a later part writes its result to the workspace (plain stores by the softmax threads, who go on at once) and
+//     the CTA's store warp, once they are all written, fences and counts the part on the item's counter;
+//   * the owner first looks at the counter: when every later part is counted, it folds them into the result it
+//     still holds in registers and writes the output (the usual case: one look, no store). Otherwise it leaves its
+//     result like the others and is counted like them;
+//   * whoever counts last while parts are in the workspace - a store warp - folds them all and writes the output
+//     rows itself (slow, rare, and the only route when the test flag takes the owner's short cut away).
+// Nobody ever waits for another CTA, so no two CTAs need to be resident together (grids of several streams may
+// share the GPU in any way) and no wait can run out.
+constexpr int kPartialFloats = kTileRows * kHeadDim + 2 * kTileRows;
+// How long an owner keeps looking at its item's counter before it gives its result to the workspace like a later
+// part. A later part is its CTA's first item, so it is counted early in that CTA's life: the look only ever takes
+// time when all CTAs have very short runs, or when the later part's CTA has not been scheduled yet.
+constexpr uint64_t kOwnerPatienceNs = 30000;
+// kItemPartial: a later part, always its CTA's first item. kItemOwner: the part with the item's first keys, always
+// its CTA's last item; the item's counter is the one of this CTA.
+enum : int { kItemWhole = 0, kItemPartial = 1, kItemOwner = 2 };
+
 // Development aid, compiled out of the shipped library: with -DB200_TRACE one lane per role of CTA 0 writes
 // clock stamps to AttnParams::trace so that the pipeline's timeline can be read back.
 #ifdef B200_TRACE
@@ -65,9 +93,18 @@ enum : uint32_t { kStatusLoader = 1, kStatusMma = 2, kStatusSoftmax = 4, kStatus
       reinterpret_cast<uint32_t*>(sm.rel_stage)[((role) * 32 + (iter)) * 8 + (slot)] = t_; \
     }                                                                              \
   } while (0)
+// Per-CTA timeline: nanosecond marks of the first softmax warp's first lane, straight to global memory.
+#define B200_MARK(k)                                                                         \
+  do {                                                                                       \
+    if (threadIdx.x == 0 && p.trace != nullptr && (k) < 32)                                  \
+      p.trace[12 * 32 * 8 + blockIdx.x * 32 + (k)] = static_cast<long long>(global_timer_ns()); \
+  } while (0)
 #else
 #define B200_STAMP(role, iter, slot) \
   do {                               \
+  } while (0)
+#define B200_MARK(k) \
+  do {               \
   } while (0)
 #endif
 // Bias forms. kBiasDecomposed14 is the decomposed form specialised for a 14 x 14 key grid (SAM's windows): both
@@ -105,11 +142,27 @@ struct AttnParams {
   int bias_vec;        // dense form: rows are 16-byte aligned, full tiles are read with vector loads
   uint32_t* status;    // device word that collects role bits of expired waits
   long long* trace;    // development builds only (B200_TRACE), else unused
+  // Key-split mode (chunked != 0; see kPairCost). pairs_per_head = q_tiles / 2 and singles_per_head = q_tiles % 2 then.
+  int chunked;
+  int pair_items, single_items;  // two-tile and one-tile items of the whole problem
+  long long cost_total;          // kv_tiles * (pair_items * kPairCost + single_items * kSingleCost)
+  float* ws_partial;             // [grid][first item / last item][query tile][kPartialFloats]
+  uint32_t* ws_counts;           // [grid][query tile]: counted parts of the item that CTA owns; 0 between launches
+  long long cost_base;           // cost_total / grid and cost_total % grid: CTA c begins at cost
+  int cost_rem;                  //   c * cost_base + min(c, cost_rem)
+  uint64_t magic_kv_tiles;       // fast_div constant of kv_tiles
+  int test_flags;                // 1: the owner never takes its short cut (every merge runs in a store warp)
 };
 
 // One CTA's share of the work (see cta_work).
 struct CtaWork {
   int pairs, singles, pair_start, pair_stride, single_start, single_stride;
+  // Key ranges. Every item runs over all kv_tiles key tiles, except, in key-split mode, the first item of a CTA
+  // (it may begin at key tile ja0: its earlier keys belong to the CTA before) and the last one (it may end at
+  // jb_last: the rest belongs to the next `last_parts` CTAs, whose partial results this CTA merges into its own).
+  int first_item, ja0, jb_last, last_parts;
+  int first_back, first_fwd;  // CTAs before / after this one that hold other parts of its first item (ja0 > 0)
+  int steps_all, steps_pairs;  // key-tile steps of all items and of the two-tile items
 };
 
 struct alignas(1024) AttnSmem {
@@ -129,6 +182,9 @@ struct alignas(1024) AttnSmem {
   uint64_t turn[2];     // the other warpgroup is half way through its exponentials: t may start (4 warps)
   uint64_t o_staged[2];      // the item's output tile t is in o_stage[t]           (4 softmax warps)
   uint64_t o_stage_free[2];  // the TMA store of that tile has read o_stage[t]       (store thread)
+  uint64_t merge_go[2];      // the owner's first thread has looked at the item's counter and set `merge_ready` (1)
+  uint32_t merge_ready[2];   // every later part of the owner's item is counted: the owner folds them in itself
+  uint32_t o_store[2][2];    // [t][item parity] what the hand-over o_staged[t] of a cut item means: 1 a staged tile, 2 a part in the workspace
   uint32_t tmem_base;
   uint32_t abort;
   CtaWork work;  // written once at set-up; kept here rather than in registers of every role
@@ -244,8 +300,12 @@ __device__ __forceinline__ void for_bias_dtype(int dtype, F&& f) {
 // n / d for the divisors the host knows at launch: magic = ceil(2^64 / d) (0 stands for d == 1), exact for every
 // n * d < 2^64. An integer division in device code takes its reciprocal from the MUFU unit, which the softmax warps
 // keep saturated; the multiply does not.
-__device__ __forceinline__ int fast_div(int n, uint64_t magic) {
+__host__ __device__ __forceinline__ int fast_div(int n, uint64_t magic) {
+#ifdef __CUDA_ARCH__
   return magic == 0 ? n : static_cast<int>(__umul64hi(static_cast<uint64_t>(static_cast<uint32_t>(n)), magic));
+#else  // the host runs the same plan for b200_attn_plan
+  return magic == 0 ? n : static_cast<int>((static_cast<unsigned __int128>(static_cast<uint32_t>(n)) * magic) >> 64);
+#endif
 }
 
 // s[i] = s[i] * c + rel_h[(KV0 + i) / 14] + rel_w[(KV0 + i) % 14] for the keys of a 14 x 14 grid that fall into this
@@ -272,21 +332,65 @@ __device__ __forceinline__ void add_rel14(float* s, const float* stage, float c)
 
 static_assert(sizeof(AttnSmem) + 1024 <= 227 * 1024, "shared memory of one CTA");
 
-// One unit of work: one or two 128-row query tiles of one (batch, head).
+// One unit of work: one or two 128-row query tiles of one (batch, head) over the key tiles [ja, jb).
 struct WorkItem {
   int b, h, q_row0, n_tiles;
+  int ja, jb;  // key tiles of this CTA's part
+  int kind;    // kItemWhole, kItemPartial (leaves its result in the workspace) or kItemOwner (merges the later parts)
 };
 
-// The items of one CTA: `pairs` two-tile items, then `singles` one-tile items (two-tile items are numbered head by
-// head, one-tile items likewise). Both kinds are dealt round robin, so that the CTAs work on neighbouring items of
-// the same heads at the same time (their K / V tiles meet in L2 and the DRAM pages in use stay few; consecutive runs
-// per CTA were measured 10 % slower on the short-sequence shapes). Every CTA's list runs from two-tile to one-tile
-// items: the second warpgroup and its MMA thread finish their last item and leave, they never have to skip one in
-// the middle (a role that skips barrier phases cannot wait on them by parity any more). One-tile items cost about
-// 0.8 of a two-tile item (a lone warpgroup is bound by the latency of its own chain), so the host mixes the two
-// kinds per head until the CTAs' loads are level, and the one-tile items go to the less loaded CTAs first.
-__device__ __forceinline__ CtaWork cta_work(const AttnParams& p, int cta, int grid) {
+// Key-split mode: the step of the line at which CTA `cta` begins (cta == grid: the end of the line).
+__host__ __device__ __forceinline__ long long chunk_bound(const AttnParams& p, int cta, int grid) {
+  (void)grid;
+  const long long cost = cta * p.cost_base + (cta < p.cost_rem ? cta : p.cost_rem);  // no division by the grid size
+  const long long pair_steps = static_cast<long long>(p.pair_items) * p.kv_tiles;
+  const long long pair_cost = pair_steps * kPairCost;
+  return cost <= pair_cost ? cost / kPairCost : pair_steps + (cost - pair_cost) / kSingleCost;
+}
+
+// The items of one CTA: `pairs` two-tile items, then `singles` one-tile items. Every CTA's list runs from two-tile
+// to one-tile items: the second warpgroup and its MMA thread finish their last item and leave, they never have to
+// skip one in the middle (a role that skips barrier phases cannot wait on them by parity any more).
+//
+// Dealt mode: two-tile items are numbered head by head, one-tile items likewise, and both kinds are dealt round
+// robin, so that the CTAs work on neighbouring items of the same heads at the same time (their K / V tiles meet in
+// L2 and the DRAM pages in use stay few; consecutive runs per CTA were measured 10 % slower on the short-sequence
+// shapes). One-tile items cost about 0.8 of a two-tile item, so the host mixes the two kinds per head until the
+// CTAs' loads are level, and the one-tile items go to the less loaded CTAs first.
+//
+// Key-split mode (long sequences, where whole items are too coarse to level 148 CTAs): see kPairCost. The only
+// divisions are by constants and by kv_tiles (a multiply): a 64-bit division here cost a microsecond of set-up.
+__host__ __device__ __forceinline__ CtaWork cta_work(const AttnParams& p, int cta, int grid) {
   CtaWork cw;
+  if (p.chunked) {
+    const long long sb = chunk_bound(p, cta, grid), se = chunk_bound(p, cta + 1, grid);
+    const int first = fast_div(static_cast<int>(sb), p.magic_kv_tiles), last = fast_div(static_cast<int>(se - 1), p.magic_kv_tiles);
+    const int items = se > sb ? last - first + 1 : 0;
+    cw.first_item = first;
+    cw.ja0 = static_cast<int>(sb - static_cast<long long>(first) * p.kv_tiles);
+    cw.jb_last = static_cast<int>(se - static_cast<long long>(last) * p.kv_tiles);
+    const int pairs_left = p.pair_items - first;
+    cw.pairs = pairs_left < 0 ? 0 : pairs_left < items ? pairs_left : items;
+    cw.singles = items - cw.pairs;
+    const long long pair_steps = static_cast<long long>(p.pair_items) * p.kv_tiles;
+    cw.steps_all = static_cast<int>(se - sb);
+    const long long pair_end = se < pair_steps ? se : pair_steps;
+    cw.steps_pairs = pair_end > sb ? static_cast<int>(pair_end - sb) : 0;
+    cw.last_parts = 0;
+    // Only a part that holds the item's first keys owns it (a run inside one item is a middle part: it owns nothing).
+    if (items > 0 && cw.jb_last < p.kv_tiles && (items > 1 || cw.ja0 == 0)) {
+      const long long item_end = static_cast<long long>(last + 1) * p.kv_tiles;
+      while (cta + 1 + cw.last_parts < grid && chunk_bound(p, cta + 1 + cw.last_parts, grid) < item_end) ++cw.last_parts;
+    }
+    cw.first_back = cw.first_fwd = 0;
+    if (items > 0 && cw.ja0 > 0) {
+      const long long item_begin = static_cast<long long>(first) * p.kv_tiles, item_end = item_begin + p.kv_tiles;
+      while (chunk_bound(p, cta - cw.first_back, grid) > item_begin) ++cw.first_back;  // bound(0) = 0 ends it
+      while (cta + 1 + cw.first_fwd < grid && chunk_bound(p, cta + 1 + cw.first_fwd, grid) < item_end) ++cw.first_fwd;
+    }
+    cw.pair_start = cw.pair_stride = cw.single_start = cw.single_stride = 0;
+    return cw;
+  }
   cw.pair_start = cta;
   cw.pair_stride = grid;
   const int nb = grid - p.split_na;  // CTAs of the second kind; their one-tile items are numbered first
@@ -302,33 +406,108 @@ __device__ __forceinline__ CtaWork cta_work(const AttnParams& p, int cta, int gr
     cw.single_start = c;
     cw.single_stride = nb;
   }
+  cw.first_item = 0;
+  cw.ja0 = 0;
+  cw.jb_last = p.kv_tiles;
+  cw.last_parts = cw.first_back = cw.first_fwd = 0;
+  cw.steps_all = (cw.pairs + cw.singles) * p.kv_tiles;
+  cw.steps_pairs = cw.pairs * p.kv_tiles;
   return cw;
 }
 
-// The it-th item of a CTA's list.
-__device__ __forceinline__ WorkItem decode_item(const AttnParams& p, const CtaWork& cw, int it) {
+// The it-th item of a CTA's list. SPLIT: the kernel form for key-split mode (the other form never meets a part
+// of an item: every item is whole and its key range a constant, and the code for parts is not even compiled).
+template <bool SPLIT>
+__host__ __device__ __forceinline__ WorkItem decode_item(const AttnParams& p, const CtaWork& cw, int it) {
   WorkItem w;
   int bh;
-  if (it < cw.pairs) {
-    const int id = cw.pair_start + it * cw.pair_stride;
+  const bool pair = it < cw.pairs;
+  if (pair) {
+    const int id = SPLIT ? cw.first_item + it : cw.pair_start + it * cw.pair_stride;
     bh = fast_div(id, p.magic_pairs);
     w.q_row0 = (id - bh * p.pairs_per_head) * 2 * kTileRows;
     w.n_tiles = 2;
   } else {
-    const int id = cw.single_start + (it - cw.pairs) * cw.single_stride;
+    const int id = SPLIT ? cw.first_item + it - p.pair_items : cw.single_start + (it - cw.pairs) * cw.single_stride;
     bh = fast_div(id, p.magic_singles);
     w.q_row0 = (2 * p.pairs_per_head + (id - bh * p.singles_per_head)) * kTileRows;
     w.n_tiles = 1;
   }
   w.b = fast_div(bh, p.magic_heads);
   w.h = bh - w.b * p.heads;
+  if (SPLIT) {
+    w.ja = it == 0 ? cw.ja0 : 0;
+    w.jb = it == cw.pairs + cw.singles - 1 ? cw.jb_last : p.kv_tiles;
+    w.kind = w.ja > 0 ? kItemPartial : w.jb < p.kv_tiles ? kItemOwner : kItemWhole;
+  } else {
+    w.ja = 0;
+    w.jb = p.kv_tiles;
+    w.kind = kItemWhole;
+  }
   return w;
+}
+
+// Workspace slot of part `part` of a cut item whose first part belongs to CTA `first_cta`: that CTA's last-item
+// slot for part 0, the first-item slot of CTA first_cta + part otherwise.
+__device__ __forceinline__ float* partial_slot(float* ws_partial, int first_cta, int part, int t) {
+  return ws_partial + ((static_cast<size_t>(first_cta + part) * 2 + (part == 0 ? 1 : 0)) * 2 + t) * kPartialFloats;
+}
+
+// One warp folds all `n_parts` parts of query tile t of item w, which are all in the workspace, and writes the
+// tile's output rows. The slow route of the key-split mode: it only runs when the owner of a cut item could not
+// fold the later parts in itself, so it is written for few registers, not for speed.
+// `out_tile`: the output element of the tile's first row and first column; `rows`: rows of the tile inside the
+// sequence; `row_stride`: elements between rows.
+template <typename T>
+__device__ __forceinline__ void merge_parts_to_output(float* ws_partial, T* out_tile, int64_t row_stride, int rows, int t,
+                                                    int first_cta, int n_parts, int lane) {
+  __threadfence();  // acquire side of the count that made this warp the last one
+  for (int rg = 0; rg < kTileRows / 32; ++rg) {
+    const int row = rg * 32 + lane;
+    float m_all = -INFINITY;
+    for (int part = 0; part < n_parts; ++part)
+      m_all = fmaxf(m_all, __ldcg(partial_slot(ws_partial, first_cta, part, t) + kTileRows * kHeadDim + row));
+    // Part 0 scaled, then every later part added with one fused multiply-add each, in part order: the order and the
+    // operations of the owner's short cut in the kernel, so that both routes give the same bits.
+    float l_all = 0.f;
+    for (int part = 0; part < n_parts; ++part) {
+      const float* slot = partial_slot(ws_partial, first_cta, part, t);
+      const float m_p = __ldcg(slot + kTileRows * kHeadDim + row);
+      const float f = m_p == m_all ? 1.f : fast_exp2(m_p - m_all);
+      const float l_p = __ldcg(slot + kTileRows * kHeadDim + kTileRows + row);
+      l_all = part == 0 ? l_p * f : fmaf(l_p, f, l_all);
+    }
+    const float inv = 1.f / l_all;
+    for (int c4 = 0; c4 < kHeadDim / 4; ++c4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int part = 0; part < n_parts; ++part) {
+        const float* slot = partial_slot(ws_partial, first_cta, part, t);
+        const float m_p = __ldcg(slot + kTileRows * kHeadDim + row);
+        const float f = m_p == m_all ? 1.f : fast_exp2(m_p - m_all);
+        const float4 x = __ldcg(reinterpret_cast<const float4*>(slot) + c4 * kTileRows + row);
+        if (part == 0) {
+          acc = make_float4(x.x * f, x.y * f, x.z * f, x.w * f);
+        } else {
+          acc.x = fmaf(x.x, f, acc.x);
+          acc.y = fmaf(x.y, f, acc.y);
+          acc.z = fmaf(x.z, f, acc.z);
+          acc.w = fmaf(x.w, f, acc.w);
+        }
+      }
+      if (row < rows) {
+        uint2 val;
+        val.x = pack2<T>(acc.x * inv, acc.y * inv);
+        val.y = pack2<T>(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(out_tile + row * row_stride + 4 * c4) = val;
+      }
+    }
+  }
 }
 
 // Persistent kernel: every CTA works through its own list of items (cta_work). All barrier phases and ring
 // positions are running counters, so the loader prefetches the next item's Q / K / V while the current one is
 // still being computed and tensor memory and barriers are set up once per CTA.
-template <typename T, int BIAS, bool SHORT>
+template <typename T, int BIAS, bool SHORT, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const AttnParams p) {
@@ -337,6 +516,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  B200_MARK(0);
 
   const int kv_tiles = p.kv_tiles;
   // Keys of the last tile, rounded up to the MMA granule: its S needs no more columns, its P V no more steps.
@@ -358,6 +538,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&sm.turn[i], 4);
       mbar_init(&sm.o_staged[i], 4);
       mbar_init(&sm.o_stage_free[i], 1);
+      mbar_init(&sm.merge_go[i], 1);
     }
     for (int i = 0; i < kStagesK; ++i) {
       mbar_init(&sm.k_full[i], 1);
@@ -392,6 +573,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // below reads or writes global memory and waits here until the earlier kernel has completed and its writes are
   // visible. Without an earlier kernel, or without the launch attribute, the wait returns at once.
   grid_dependency_wait();
+  B200_MARK(1);
   const uint32_t tmem = sm.tmem_base;
   volatile uint32_t* abort_flag = &sm.abort;
   const CtaWork& cw = sm.work;
@@ -406,7 +588,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         int gk = 0, gv = 0;        // K / V tiles issued so far (ring position and phase)
         int q_count[2] = {0, 0};   // Q tiles issued so far per query-tile slot
         for (int it = 0; it < my_items && ok; ++it) {
-          const WorkItem w = decode_item(p, cw, it);
+          const WorkItem w = decode_item<SPLIT>(p, cw, it);
           const int slot = it & 1;
           for (int t = 0; t < w.n_tiles && ok; ++t) {
             ok = mbar_wait_relaxed(&sm.q_empty[t][slot], ((it >> 1) & 1) ^ 1, abort_flag);
@@ -415,22 +597,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tma_load_4d(sm.q[t][slot], &tm_q, &sm.q_full[t][slot], 0, w.q_row0 + t * kTileRows, w.h, w.b);
             q_count[t] = it + 1;
           }
-          for (int i = 0; i < kv_tiles + kKLead && ok; ++i) {
-            if (i < kv_tiles) {
+          const int steps = w.jb - w.ja;  // the key tiles of this CTA's part of the item
+          for (int i = 0; i < steps + kKLead && ok; ++i) {
+            if (i < steps) {
               const int st = gk % kStagesK;
               ok = mbar_wait_relaxed(&sm.k_empty[st], ((gk / kStagesK) & 1) ^ 1, abort_flag);
               if (!ok) break;
               mbar_arrive_expect_tx(&sm.k_full[st], kTileBytes);
-              tma_load_4d(sm.k[st], &tm_k, &sm.k_full[st], 0, i * kTileRows, w.h, w.b);
+              tma_load_4d(sm.k[st], &tm_k, &sm.k_full[st], 0, (w.ja + i) * kTileRows, w.h, w.b);
               ++gk;
             }
-            const int jv = i - kKLead;
-            if (jv >= 0) {
+            const int iv = i - kKLead;
+            if (iv >= 0) {
               const int st = gv % kStagesV;
               ok = mbar_wait_relaxed(&sm.v_empty[st], ((gv / kStagesV) & 1) ^ 1, abort_flag);
               if (!ok) break;
               mbar_arrive_expect_tx(&sm.v_full[st], kTileBytes);
-              tma_load_4d(sm.v[st], &tm_v, &sm.v_full[st], 0, jv * kTileRows, w.h, w.b);
+              tma_load_4d(sm.v[st], &tm_v, &sm.v_full[st], 0, (w.ja + iv) * kTileRows, w.h, w.b);
               ++gv;
             }
           }
@@ -482,22 +665,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // at once. The positions are counted along: a division by kv_tiles here would queue its reciprocal behind the
         // softmax warps' exponentials on the MUFU unit, which cost the long-sequence runs 15 %.
         const int my_doubles = cw.pairs;
-        const int total_steps = (t == 0 ? my_items : my_doubles) * kv_tiles;
+        const int total_steps = t == 0 ? cw.steps_all : cw.steps_pairs;
+        // `j` is the key tile and `jend` where this CTA's part of the item ends (the part starts at key tile 0
+        // except, in key-split mode, for the CTA's first item).
         struct Pos {
-          int gs, it, j, st;
+          int gs, it, j, jend, st;
           uint32_t ph;
         };
+        const int ja0 = SPLIT ? cw.ja0 : 0, jb_last = cw.jb_last;
+        // Without key split every part is a whole item: `jend` is never read and costs no register.
+        auto is_first = [&](const Pos& x) { return SPLIT ? x.j == (x.it == 0 ? ja0 : 0) : x.j == 0; };
+        auto is_last = [&](const Pos& x) { return SPLIT ? x.j == x.jend - 1 : x.j == kv_tiles - 1; };
         auto advance = [&](Pos& x) {
           ++x.gs;
-          if (++x.j == kv_tiles) {
+          if (SPLIT ? ++x.j == x.jend : ++x.j == kv_tiles) {
             x.j = 0;
             ++x.it;
+            x.jend = x.it == my_items - 1 ? jb_last : kv_tiles;
           }
           if (++x.st == kStagesK) {
             x.st = 0;
             x.ph ^= 1;
           }
         };
+        const Pos start = {0, 0, ja0, my_items == 1 ? jb_last : kv_tiles, 0, 0u};
         static_assert(kStagesK == kStagesV, "one ring position serves both rings");
 
         // S_t(gs) = Q_t K^T. The last key tile of an item only computes the columns that hold keys.
@@ -505,7 +696,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           const int slot = x.it & 1;
           // The K tile landed long ago as a rule: its test is issued first and runs behind the wait that does wait.
           const bool k_early = mbar_test_wait(&sm.k_full[x.st], x.ph);
-          if (x.j == 0 && !mbar_wait(&sm.q_full[t][slot], (x.it >> 1) & 1, abort_flag)) return false;
+          if (is_first(x) && !mbar_wait(&sm.q_full[t][slot], (x.it >> 1) & 1, abort_flag)) return false;
           if (x.gs > 0 && !mbar_wait(s_free, (x.gs - 1) & 1, abort_flag)) return false;  // S_t has been read
           if (!k_early && !mbar_wait(&sm.k_full[x.st], x.ph, abort_flag)) return false;
           tc_fence_after_sync();
@@ -519,7 +710,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           umma_commit(s_full);
           umma_commit(&sm.k_empty[x.st]);
           if (x.it >= my_doubles) umma_commit(&sm.k_empty[x.st]);  // one-tile item: stand in for the absent second tile
-          if (x.j == kv_tiles - 1) umma_commit(&sm.q_empty[t][slot]);  // the item's last reader of Q_t
+          if (is_last(x)) umma_commit(&sm.q_empty[t][slot]);  // the item's last reader of Q_t
           B200_STAMP(2 + t, x.gs, 3);
           return true;
         };
@@ -529,18 +720,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (!mbar_wait(p_full, x.gs & 1, abort_flag)) return false;
           if (!v_early && !mbar_wait(&sm.v_full[x.st], x.ph, abort_flag)) return false;
           // The first P V of an item overwrites O_t: the previous item's epilogue must have read it.
-          if (x.j == 0 && x.it > 0 && !mbar_wait(&sm.o_free[t], (x.it - 1) & 1, abort_flag)) return false;
+          if (is_first(x) && x.it > 0 && !mbar_wait(&sm.o_free[t], (x.it - 1) & 1, abort_flag)) return false;
           tc_fence_after_sync();
           B200_STAMP(2 + t, x.gs, 0);
           const uint64_t bd = v_desc0 + static_cast<uint64_t>(x.st) * kStageStep;
           if (x.j != kv_tiles - 1) {
-            umma_ts(o_tm, p_tm, bd, idesc_pv, x.j > 0 ? 1u : 0u);
+            umma_ts(o_tm, p_tm, bd, idesc_pv, is_first(x) ? 0u : 1u);
 #pragma unroll
             for (int kk = 1; kk < kTileRows / 16; ++kk)
               umma_ts(o_tm, p_tm + kk * 8, bd + kk * (2048 >> 4), idesc_pv, 1u);
           } else {
             const int steps = kv_last16 / 16;  // at least one
-            umma_ts(o_tm, p_tm, bd, idesc_pv, x.j > 0 ? 1u : 0u);
+            umma_ts(o_tm, p_tm, bd, idesc_pv, is_first(x) ? 0u : 1u);
 #pragma unroll
             for (int kk = 1; kk < kTileRows / 16; ++kk)
               if (kk < steps) umma_ts(o_tm, p_tm + kk * 8, bd + kk * (2048 >> 4), idesc_pv, 1u);
@@ -552,12 +743,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           return true;
         };
 
-        Pos xq = {0, 0, 0, 0, 0u};  // the Q K^T stream runs two steps ahead of the P V stream
+        Pos xq = start;  // the Q K^T stream runs two steps ahead of the P V stream
         for (int i = 0; i < 2 && xq.gs < total_steps && ok; ++i) {
           ok = issue_qk(xq);
           advance(xq);
         }
-        for (Pos xp = {0, 0, 0, 0, 0u}; xp.gs < total_steps && ok; advance(xp)) {
+        for (Pos xp = start; xp.gs < total_steps && ok; advance(xp)) {
           ok = issue_pv(xp);
           if (ok && xq.gs < total_steps) {
             ok = issue_qk(xq);
@@ -571,29 +762,85 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       __syncwarp();
     } else if (warp == kStoreWarp) {
       // ======================= output stores ====================================================
-      // One thread sends each finished output tile from its staging buffer to global memory with a TMA store (rows
+      // Lane 0 sends each finished output tile from its staging buffer to global memory with a TMA store (rows
       // past the end of the sequence are clipped by the tensor map) and hands the buffer back once it has been read.
-      if (lane == 0) {
+      // For a part of an item that is cut along the keys the hand-over may instead mean "the part is in the
+      // workspace": lane 0 then fences and counts it, and if that made the item complete the whole warp folds
+      // the parts and writes the output rows (see kPartialFloats).
+      if constexpr (!SPLIT) {
+        if (lane == 0) {
+          bool ok = true;
+          for (int it = 0; it < my_items && ok; ++it) {
+            const WorkItem w = decode_item<SPLIT>(p, cw, it);
+            for (int t = 0; t < w.n_tiles && ok; ++t) {
+              // Slot 1's items are a prefix of the CTA's list, so this is the it-th use of either slot's buffer.
+              ok = mbar_wait(&sm.o_staged[t], it & 1, abort_flag);
+              if (!ok) break;
+              tma_store_4d(&tm_o, sm.o_stage[t], 0, w.q_row0 + t * kTileRows, w.h, w.b);
+              tma_store_commit();
+            }
+            // The buffers are not needed again before the next item's epilogue: one wait for both stores.
+            tma_store_wait_read<0>();
+            for (int t = 0; t < w.n_tiles && ok; ++t) mbar_arrive(&sm.o_stage_free[t]);
+          }
+          // Every store has read its buffer by now (the wait above); the writes themselves complete with the kernel.
+          if (!ok) {
+            if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusStore);
+          }
+        }
+        __syncwarp();
+      } else {
         bool ok = true;
         for (int it = 0; it < my_items && ok; ++it) {
-          const WorkItem w = decode_item(p, cw, it);
+          const WorkItem w = decode_item<SPLIT>(p, cw, it);
           for (int t = 0; t < w.n_tiles && ok; ++t) {
-            // Slot 1's items are a prefix of the CTA's list, so this is the it-th use of either slot's buffer.
-            ok = mbar_wait(&sm.o_staged[t], it & 1, abort_flag);
-            if (!ok) break;
-            tma_store_4d(&tm_o, sm.o_stage[t], 0, w.q_row0 + t * kTileRows, w.h, w.b);
-            tma_store_commit();
+            uint32_t what = 1;
+            if (lane == 0) {
+              ok = mbar_wait(&sm.o_staged[t], it & 1, abort_flag);
+              if (ok && w.kind != kItemWhole) what = *reinterpret_cast<volatile uint32_t*>(&sm.o_store[t][it & 1]);
+              if (ok && what == 1) {
+                tma_store_4d(&tm_o, sm.o_stage[t], 0, w.q_row0 + t * kTileRows, w.h, w.b);
+                tma_store_commit();
+              }
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            what = __shfl_sync(0xffffffffu, what, 0);
+            if (!ok || w.kind == kItemWhole) continue;
+            const bool owner = w.kind == kItemOwner;
+            const int first_cta = owner ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x) - cw.first_back;
+            const int n_parts = owner ? 1 + cw.last_parts : cw.first_back + 1 + cw.first_fwd;
+            uint32_t* counter = p.ws_counts + first_cta * 2 + t;
+            if (what == 1) {  // the owner folded the later parts in itself: only the counter is left to clear
+              if (lane == 0) *counter = 0u;
+              continue;
+            }
+            uint32_t last = 0;
+            if (lane == 0) {
+              __threadfence();  // the softmax threads' stores, ordered before the hand-over, before the count
+              last = atomicAdd(counter, 1u) == static_cast<uint32_t>(n_parts - 1) ? 1u : 0u;
+              if (last) {
+                __threadfence();
+                *counter = 0u;  // nobody else touches it any more: ready for the next launch
+              }
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+              const int row0 = w.q_row0 + t * kTileRows;
+              T* out_tile = static_cast<T*>(p.o) + w.b * p.o_sb + static_cast<int64_t>(row0) * p.o_sn + w.h * p.o_sh;
+              merge_parts_to_output<T>(p.ws_partial, out_tile, p.o_sn, p.q_tokens - row0, t, first_cta, n_parts, lane);
+            }
           }
-          // The buffers are not needed again before the next item's epilogue: one wait for both stores.
-          tma_store_wait_read<0>();
-          for (int t = 0; t < w.n_tiles && ok; ++t) mbar_arrive(&sm.o_stage_free[t]);
+          if (lane == 0) {
+            tma_store_wait_read<0>();
+            for (int t = 0; t < w.n_tiles && ok; ++t) mbar_arrive(&sm.o_stage_free[t]);
+          }
+          __syncwarp();
         }
-        // Every store has read its buffer by now (the wait above); the writes themselves complete with the kernel.
-        if (!ok) {
+        if (!ok && lane == 0) {
           if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusStore);
         }
+        __syncwarp();
       }
-      __syncwarp();
     }
   } else {
     // ======================= softmax warpgroups ================================================
@@ -610,21 +857,108 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     bool ok = true;
     bool bad = false;  // this lane gave up a wait since the last vote
     bool s_early = false, pv_early = false, stage_early = false;  // early barrier tests (see the step loop)
-    // Epilogue of the previous item, still to be done: its last P V phase, 1 / row sum, output row (or null).
+    // Epilogue of the previous item, still to be done: its last P V phase, reference maximum, row sum, kind.
     bool pend = false;
     uint32_t pend_phase = 0;
-    float pend_inv = 0.f;
+    float pend_l = 0.f;
+    float pend_m_of_split = 0.f;  // key-split form only: the pending item's reference maximum
     int pend_it = 0;
     // O_t / l -> staging buffer -> (store thread) global for the pending item; frees O_t for the next item's first P V.
     // Each thread writes its 128-byte row as eight 16-byte chunks at the positions of the 128-byte swizzle.
     // `pv_tested`, `stage_tested`: results of early tests of the two barriers (false = not tested or still pending).
-    auto finish_item = [&](bool pv_tested, bool stage_tested) -> bool {
+    // A part of an item that is cut along the keys (key-split mode) either folds the other parts into its O_t and
+    // row sum and goes on as usual, or leaves O_t, the reference maxima and the row sums in the workspace.
+    // `at_end`: the call after the CTA's last item, the only one that can meet an owner (the calls inside the step
+    // loop finish an item that has a successor): the owner's code is compiled into that one call only.
+    auto finish_item = [&](bool pv_tested, bool stage_tested, auto at_end) -> bool {
+      [[maybe_unused]] constexpr bool kAtEnd = decltype(at_end)::value;
+      B200_MARK(12 + 2 * pend_it);
       if (!__all_sync(0xffffffffu, pv_tested || mbar_wait(&sm.pv_done[t], pend_phase, abort_flag))) return false;
       tc_fence_after_sync();
       float o[kHeadDim];
       tmem_ld_x64(o_addr, reinterpret_cast<uint32_t*>(o));
       tc_fence_before_sync();
       warp_arrive(&sm.o_free[t], lane);
+      float l_all = pend_l;
+      if constexpr (SPLIT) {
+        // Which kind of item the pending one is follows from its place in the list (first: a later part if it
+        // begins past key tile 0; last: the owner if it ends early) - nothing is carried along in registers.
+        const bool later_part = pend_it == 0 && cw.ja0 > 0;
+        const bool owner = kAtEnd && !later_part && pend_it == my_items - 1 && cw.jb_last < kv_tiles;
+        if (later_part || owner) {  // CTA-uniform: a part of an item that is cut along the keys (see kPartialFloats)
+          const int first_cta = owner ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x) - cw.first_back;
+          const int n_parts = owner ? 1 + cw.last_parts : cw.first_back + 1 + cw.first_fwd;
+          const float m_own = pend_m_of_split;
+          bool fold = false;
+          if constexpr (kAtEnd) if (owner && (p.test_flags & 1) == 0) {
+            // The tile's first thread looks at the item's counter - for a while, when the later parts are not all
+            // counted yet (CTAs with short runs finish together) - and passes the result on through shared memory.
+            if (row_in_tile == 0) {
+              const uint32_t* counter = p.ws_counts + first_cta * 2 + t;
+              bool ready = ld_acquire_gpu(counter) == static_cast<uint32_t>(n_parts - 1);
+              if (!ready) {
+                const uint64_t t0 = global_timer_ns();
+                while (!ready && global_timer_ns() - t0 < kOwnerPatienceNs) {
+                  __nanosleep(200);
+                  ready = ld_acquire_gpu(counter) == static_cast<uint32_t>(n_parts - 1);
+                }
+              }
+              sm.merge_ready[t] = ready ? 1u : 0u;
+              mbar_arrive(&sm.merge_go[t]);
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(&sm.merge_go[t], 0, abort_flag))) return false;  // used once per CTA
+            fold = *reinterpret_cast<volatile uint32_t*>(&sm.merge_ready[t]) != 0;
+          }
+          if (kAtEnd && fold) {
+            // The same arithmetic, in the same order, as merge_parts_to_output: whichever route an item takes, its
+            // output has the same bits.
+            __threadfence();  // the later parts' results, counted before the look, before these loads
+            float m_all = m_own;
+            for (int part = 1; part < n_parts; ++part)
+              m_all = fmaxf(m_all, __ldcg(partial_slot(p.ws_partial, first_cta, part, t) + kTileRows * kHeadDim + row_in_tile));
+            const float f_own = m_own == m_all ? 1.f : fast_exp2(m_own - m_all);
+            l_all = pend_l * f_own;
+#pragma unroll
+            for (int i = 0; i < kHeadDim; ++i) o[i] *= f_own;
+            for (int part = 1; part < n_parts; ++part) {
+              const float* slot = partial_slot(p.ws_partial, first_cta, part, t);
+              const float m_p = __ldcg(slot + kTileRows * kHeadDim + row_in_tile);
+              const float f = m_p == m_all ? 1.f : fast_exp2(m_p - m_all);
+              l_all = fmaf(__ldcg(slot + kTileRows * kHeadDim + kTileRows + row_in_tile), f, l_all);
+              const float4* src4 = reinterpret_cast<const float4*>(slot) + row_in_tile;
+#pragma unroll
+              for (int c4 = 0; c4 < kHeadDim / 4; ++c4) {
+                const float4 x = __ldcg(src4 + c4 * kTileRows);
+                o[4 * c4 + 0] = fmaf(x.x, f, o[4 * c4 + 0]);
+                o[4 * c4 + 1] = fmaf(x.y, f, o[4 * c4 + 1]);
+                o[4 * c4 + 2] = fmaf(x.z, f, o[4 * c4 + 2]);
+                o[4 * c4 + 3] = fmaf(x.w, f, o[4 * c4 + 3]);
+              }
+            }
+            if (row_in_tile == 0) sm.o_store[t][pend_it & 1] = 1u;
+          } else {
+            float* slot = partial_slot(p.ws_partial, first_cta, static_cast<int>(blockIdx.x) - first_cta, t);
+            float4* dst = reinterpret_cast<float4*>(slot) + row_in_tile;
+#pragma unroll
+            for (int c4 = 0; c4 < kHeadDim / 4; ++c4)
+              __stcg(dst + c4 * kTileRows, make_float4(o[4 * c4], o[4 * c4 + 1], o[4 * c4 + 2], o[4 * c4 + 3]));
+            __stcg(slot + kTileRows * kHeadDim + row_in_tile, m_own);
+            __stcg(slot + kTileRows * kHeadDim + kTileRows + row_in_tile, pend_l);
+            if (row_in_tile == 0) sm.o_store[t][pend_it & 1] = 2u;
+            // The hand-over now means "the part is in the workspace": the store warp fences and counts it. Like a
+            // staged tile it must not come before the store warp is done with the item before (it may be folding
+            // parts for a long time): waits by parity tell only neighbouring phases of a barrier apart.
+            if (pend_it > 0 &&
+                !__all_sync(0xffffffffu, stage_tested || mbar_wait(&sm.o_stage_free[t], (pend_it - 1) & 1, abort_flag)))
+              return false;
+            warp_arrive(&sm.o_staged[t], lane);
+            B200_MARK(13 + 2 * pend_it);
+            pend = false;
+            return true;
+          }
+        }
+      }
+      const float inv = 1.f / l_all;
       // The buffer's previous tile (the item before the pending one) must have been read by its store.
       if (pend_it > 0 &&
           !__all_sync(0xffffffffu, stage_tested || mbar_wait(&sm.o_stage_free[t], (pend_it - 1) & 1, abort_flag)))
@@ -633,25 +967,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
       for (int ch = 0; ch < kHeadDim / 8; ++ch) {
         uint4 val;
-        val.x = pack2<T>(o[ch * 8 + 0] * pend_inv, o[ch * 8 + 1] * pend_inv);
-        val.y = pack2<T>(o[ch * 8 + 2] * pend_inv, o[ch * 8 + 3] * pend_inv);
-        val.z = pack2<T>(o[ch * 8 + 4] * pend_inv, o[ch * 8 + 5] * pend_inv);
-        val.w = pack2<T>(o[ch * 8 + 6] * pend_inv, o[ch * 8 + 7] * pend_inv);
+        val.x = pack2<T>(o[ch * 8 + 0] * inv, o[ch * 8 + 1] * inv);
+        val.y = pack2<T>(o[ch * 8 + 2] * inv, o[ch * 8 + 3] * inv);
+        val.z = pack2<T>(o[ch * 8 + 4] * inv, o[ch * 8 + 5] * inv);
+        val.w = pack2<T>(o[ch * 8 + 6] * inv, o[ch * 8 + 7] * inv);
         st_shared_v4(row + ((ch ^ (row_in_tile & 7)) << 4), val);
       }
       fence_proxy_async_smem();  // the TMA store reads what these generic-proxy stores wrote
       warp_arrive(&sm.o_staged[t], lane);
+      B200_MARK(13 + 2 * pend_it);
       pend = false;
       return true;
     };
 
     for (int it = 0; it < my_items && ok; ++it) {
-      const WorkItem w = decode_item(p, cw, it);
+      const WorkItem w = decode_item<SPLIT>(p, cw, it);
       if (t >= w.n_tiles) break;  // only one-tile items follow
       const int b = w.b, h = w.h;
       const int q_row = w.q_row0 + t * kTileRows + row_in_tile;
       const bool row_valid = q_row < p.q_tokens;
       const bool pingpong = w.n_tiles == 2;
+      const int ja = w.ja, jb = w.jb;  // this CTA's key tiles of the item
       float m_ref = -INFINITY;
       float l_sum = 0.f;
 
@@ -689,7 +1025,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           uint4 v[8];
 #pragma unroll
           for (int u = 0; u < 8; ++u) v[u] = __ldg(src + u);
-          rh_cur = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias.ptr) + bias_row));
+          // rel_h comes in groups of eight values, each good for four key tiles: the part's first group now, the
+          // one after it too (the loop fetches a group four tiles ahead, at every fourth tile).
+          const uint4* rh_src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias.ptr) + bias_row);
+          rh_cur = __ldg(rh_src + (ja >> 2));
+          if (2 * ((ja & ~3) + 4) < p.rel_kh) rh_nxt = __ldg(rh_src + (ja >> 2) + 1);
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             stage[u * 4 + 0] = v[u].x;
@@ -719,8 +1059,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
 
-      for (int j = 0; j < kv_tiles; ++j) {
-        const int step = g + j;
+      for (int j = ja; j < jb; ++j) {
+        const int rj = j - ja;  // step within this CTA's part of the item
+        const int step = g + rj;
         // One vote per step on whether any lane's wait ran out during the previous one.
         if (__any_sync(0xffffffffu, bad)) {
           ok = false;
@@ -728,6 +1069,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         bad |= !mbar_wait_warp_after(s_early, &sm.s_full[t], step & 1, abort_flag);
         tc_fence_after_sync();
+        if (step == 0) B200_MARK(2);
         if ((warp & 3) == 0) B200_STAMP(t, step, 0);
 
         float s[kTileRows];
@@ -747,8 +1089,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // Tests of the barriers this step will wait on, issued here so that their latency (100-150 clocks each with
         // tensor memory allocated) runs behind the arithmetic; a test that finds its phase pending is repeated as a
         // real wait where the result is needed.
-        const bool need_turn = pingpong && (t == 1 || gp + j > 0);
-        const uint32_t turn_parity = (t == 0) ? ((gp + j - 1) & 1) : ((gp + j) & 1);
+        const bool need_turn = pingpong && (t == 1 || gp + rj > 0);
+        const uint32_t turn_parity = (t == 0) ? ((gp + rj - 1) & 1) : ((gp + rj) & 1);
         const bool turn_early = need_turn ? mbar_test_wait(&sm.turn[t], turn_parity) : true;
 
         const int kv0 = j * kTileRows;
@@ -794,8 +1136,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // factor log2(e) rides on the FMA in front of the exponential, and rel_h, constant over each 64-column
           // half, is added to that half's maximum and to that FMA's addend instead of to every column.
           const int jj = j & 3;
-          if (jj == 0) {
-            if (j > 0) rh_cur = rh_nxt;
+          if (jj == 0 && j > ja) {
+            rh_cur = rh_nxt;
             if (2 * (j + 4) < p.rel_kh)  // rel_kh is a multiple of 8 in this form: the group is inside the row
               rh_nxt = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias.ptr) + bias_row) + (j >> 2) + 1);
           }
@@ -928,8 +1270,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (pingpong) warp_arrive_pinned(&sm.turn[t ^ 1], lane, nm);
           // On an item's first tile the P V in question is the last one of the pending item (same barrier, and
           // (step - 1) & 1 is that item's last phase), waited for by its epilogue together with the staging buffer.
-          pv_early = (j > 0 || pend) ? mbar_test_wait(&sm.pv_done[t], (step - 1) & 1) : true;
-          stage_early = (j == 0 && pend && pend_it > 0) ? mbar_test_wait(&sm.o_stage_free[t], (pend_it - 1) & 1) : false;
+          pv_early = (rj > 0 || pend) ? mbar_test_wait(&sm.pv_done[t], (step - 1) & 1) : true;
+          stage_early = (rj == 0 && pend && pend_it > 0) ? mbar_test_wait(&sm.o_stage_free[t], (pend_it - 1) & 1) : false;
           s_early = mbar_test_wait(&sm.s_full[t], (step + 1) & 1);  // the next step's S (unused after the last step)
         };
         // Exponentials of 32 * CHUNKS columns from column 32 * FIRST on.
@@ -976,9 +1318,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // delivered P_t(j-1), a whole exponential section ago. On the first tile of an item the P V in
         // question is the last one of the previous item, and this is where that item's output is written:
         // its epilogue hides behind this item's first exponentials instead of stalling the pipeline.
-        if (j == 0) {
+        if (rj == 0) {
           if (pend) {
-            ok = finish_item(pv_early, stage_early);
+            ok = finish_item(pv_early, stage_early, std::false_type{});
             if (!ok) break;
           }
         } else {
@@ -1008,15 +1350,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         break;
       }
 
+      B200_MARK(3 + it);
       // The item's output is written later (see above); remember what its epilogue needs.
       pend = true;
-      pend_phase = (g + kv_tiles - 1) & 1;
-      pend_inv = 1.f / l_sum;
+      pend_phase = (g + (jb - ja) - 1) & 1;
+      pend_l = l_sum;
+      if constexpr (SPLIT) pend_m_of_split = m_ref;
       pend_it = it;
-      g += kv_tiles;
-      if (w.n_tiles == 2) gp += kv_tiles;
+      g += jb - ja;
+      if (w.n_tiles == 2) gp += jb - ja;
     }
-    if (ok && pend) ok = finish_item(false, false);
+    if (ok && pend) ok = finish_item(false, false, std::true_type{});
     if (!ok && lane == 0) {
       if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusSoftmax);
     }
@@ -1025,6 +1369,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // ---- common exit ----------------------------------------------------------------------------
   tc_fence_before_sync();
   __syncthreads();
+  B200_MARK(31);
 #ifdef B200_TRACE
   if (blockIdx.x == 0 && p.trace != nullptr)
     for (int i = threadIdx.x; i < 12 * 32 * 8; i += kThreads) p.trace[i] = reinterpret_cast<uint32_t*>(sm.rel_stage)[i];

@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <cstdarg>
@@ -173,8 +174,13 @@ int validate(const B200AttnArgs* a, int* bias_mode, int* schedule) {
     *bias_mode = kBiasDecomposed;
   }
 
+  if (a->workspace != nullptr && (reinterpret_cast<uintptr_t>(a->workspace) & 255) != 0)
+    return fail(B200_ATTN_UNSUPPORTED, "workspace is not 256-byte aligned");
+  if (a->workspace_bytes < 0 || (a->workspace == nullptr && a->workspace_bytes != 0))
+    return fail(B200_ATTN_BAD_CONFIG, "workspace_bytes %lld without a workspace", static_cast<long long>(a->workspace_bytes));
   if (a->schedule < B200_ATTN_SCHED_AUTO || a->schedule > B200_ATTN_SCHED_SHORT)
     return fail(B200_ATTN_BAD_CONFIG, "schedule %d unknown", a->schedule);
+  if (a->test_flags != 0 && a->test_flags != 1) return fail(B200_ATTN_BAD_CONFIG, "test_flags %d unknown", a->test_flags);
   // Short schedule: at most two key tiles and a last one whose final 32 columns hold no key (its exponentials are skipped).
   const int kv_tiles = (a->kv_tokens + kTileRows - 1) / kTileRows;
   const int kv_last = a->kv_tokens - (kv_tiles - 1) * kTileRows;
@@ -188,7 +194,7 @@ int validate(const B200AttnArgs* a, int* bias_mode, int* schedule) {
 // status word and which kernels already have their shared-memory opt-in (the opt-in is per device and per kernel).
 // The runtime calls behind these cost more than the rest of the host path of a launch-bound call.
 constexpr int kMaxDevices = 64;
-constexpr int kKernelForms = 20;  // 2 dtypes x 5 bias forms x 2 schedules
+constexpr int kKernelForms = 30;  // 2 dtypes x 5 bias forms x (short, long, long with key split)
 struct DeviceState {
   std::atomic<bool> ready{false};
   int sms = 0;
@@ -222,23 +228,20 @@ int device_state(DeviceState** out) {
 
 // Cost of a one-tile item in units of a two-tile item of the same head (measured: a lone softmax warpgroup takes
 // 2.8 k clocks per key tile, two interleaved ones 3.6 k for both tiles).
-constexpr double kSingleCost = 0.8;
+constexpr double kDealtSingleCost = 0.8;
 
 // Split the query tiles of every (batch, head) into two-tile and one-tile items and deal them to the CTAs so that
 // the most loaded CTA finishes as early as possible. Candidates: every count of two-tile items per head from
 // q_tiles / 2 down; for each, the two-tile items go to the CTAs in consecutive runs of k or k + 1 and the one-tile
 // items fill up the less loaded CTAs first. Fills the split fields of `prm` and returns the grid size.
-unsigned plan_split(AttnParams& prm, long long heads_total, int sms) {
+unsigned plan_split(AttnParams& prm, long long heads_total, int sms, double* span_out) {
   const int tiles = prm.q_tiles;
   double best_span = 0;
   int best_pairs = -1;
   struct Plan {
     int grid, na, ka, kb, a, ea, b, eb;
   } best{}, cur{};
-  int first = tiles / 2, last = tiles / 2 - 8;
-#ifdef B200_TUNE
-  if (const char* forced = std::getenv("B200_SPLIT_PAIRS")) first = last = std::atoi(forced);  // development builds only
-#endif
+  const int first = tiles / 2, last = tiles / 2 - 8;
   for (int pairs = first; pairs >= 0 && pairs >= last; --pairs) {
     const long long P = pairs * heads_total, S = (tiles - 2LL * pairs) * heads_total;
     const long long grid = P + S < sms ? P + S : sms;
@@ -251,8 +254,8 @@ unsigned plan_split(AttnParams& prm, long long heads_total, int sms) {
     const long long nb = grid - cur.na;
     long long a = 0, b = 0, ea = 0, eb = 0, left = S;
     while (left > 0) {
-      const double level_a = cur.na > 0 ? cur.ka + kSingleCost * a : 1e300;
-      const double level_b = nb > 0 ? cur.kb + kSingleCost * b : 1e300;
+      const double level_a = cur.na > 0 ? cur.ka + kDealtSingleCost * a : 1e300;
+      const double level_b = nb > 0 ? cur.kb + kDealtSingleCost * b : 1e300;
       if (level_b <= level_a) {
         if (left >= nb) { ++b; left -= nb; } else { eb = left; left = 0; }
       } else {
@@ -261,8 +264,8 @@ unsigned plan_split(AttnParams& prm, long long heads_total, int sms) {
     }
     cur.a = static_cast<int>(a); cur.ea = static_cast<int>(ea); cur.b = static_cast<int>(b); cur.eb = static_cast<int>(eb);
     double span = 0;
-    if (cur.na > 0) span = std::fmax(span, cur.ka + kSingleCost * (a + (ea > 0 ? 1 : 0)));
-    if (nb > 0) span = std::fmax(span, cur.kb + kSingleCost * (b + (eb > 0 ? 1 : 0)));
+    if (cur.na > 0) span = std::fmax(span, cur.ka + kDealtSingleCost * (a + (ea > 0 ? 1 : 0)));
+    if (nb > 0) span = std::fmax(span, cur.kb + kDealtSingleCost * (b + (eb > 0 ? 1 : 0)));
     if (best_pairs < 0 || span < best_span - 1e-9) {
       best_span = span;
       best_pairs = pairs;
@@ -275,15 +278,69 @@ unsigned plan_split(AttnParams& prm, long long heads_total, int sms) {
   prm.split_a = best.a; prm.split_ea = best.ea; prm.split_b = best.b; prm.split_eb = best.eb;
   prm.magic_pairs = div_magic(prm.pairs_per_head);
   prm.magic_singles = div_magic(prm.singles_per_head);
+  *span_out = best_span;
   return static_cast<unsigned>(best.grid);
 }
 
-template <typename T, int BIAS, bool SHORT>
-int launch(const B200AttnArgs* a, const AttnParams& prm, DeviceState& dev, const CUtensorMap& mq,
-           const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, cudaStream_t stream) {
-  auto kernel = attn_fwd_kernel<T, BIAS, SHORT>;
+// Bytes of workspace per CTA of a key-split launch (partial results), and where the items' counters begin.
+constexpr size_t kPartialBytes = 4 * static_cast<size_t>(kPartialFloats) * sizeof(float);  // first / last item x two query tiles
+size_t workspace_flags_offset(int sms) { return static_cast<size_t>(sms) * kPartialBytes; }
+size_t workspace_bytes_for(int sms) { return (workspace_flags_offset(sms) + static_cast<size_t>(sms) * 2 * sizeof(uint32_t) + 255) & ~size_t(255); }
+
+// Key-split plan (the kernel's cta_work has the other half): all key-tile steps in one line, cut into one run per
+// CTA by cost. Worth it only where whole items level badly: `dealt_span` is the longest list of the dealt plan in
+// two-tile items. Both plans are compared in key-tile steps of a two-tile item, with what was measured on B200
+// ([4,16,1370,64]: 63 -> 61 us, [1,12,4096,64]: 108 -> 88 us, [2,16,1370,64]: 41 -> 36 us; [8,6,1370,64], whose
+// dealt plan is within 7 % of level, 45 -> 50 us): a step of the key-split kernel takes 6 % longer, a run costs
+// about two steps for its merges on top of half a step for every item it starts, and runs of fewer than eight
+// steps are all set-up and merge (the grid shrinks rather than cut finer).
+// Returns the grid size, or 0 when the dealt plan stays.
+constexpr int kMinRunSteps = 8;
+constexpr double kSplitStepFactor = 1.06, kSplitMergeSteps = 2.0;
+unsigned plan_chunks(AttnParams& prm, const B200AttnArgs* a, long long heads_total, int sms, double dealt_span) {
+  if (a->workspace == nullptr || prm.kv_tiles < 3) return 0;
+  if (static_cast<size_t>(a->workspace_bytes) < workspace_bytes_for(sms)) return 0;
+  const long long pairs = (prm.q_tiles / 2) * heads_total, singles = (prm.q_tiles % 2) * heads_total;
+  if ((pairs + singles) * prm.kv_tiles > 0x3fffffffLL) return 0;  // steps are counted in 32 bits
+  const long long cost = prm.kv_tiles * (pairs * kPairCost + singles * b200::kSingleCost);
+  const long long grid = std::min<long long>(sms, std::max<long long>(1, cost / (kMinRunSteps * kPairCost)));
+  const double items_dealt = std::ceil(dealt_span);
+  const double dealt = dealt_span * prm.kv_tiles + 0.5 * items_dealt;
+  const double run = static_cast<double>(cost) / kPairCost / static_cast<double>(grid);
+  const double chunked = kSplitStepFactor * run + 0.5 * (run / prm.kv_tiles + 1.0) + kSplitMergeSteps;
+  if (chunked > 0.97 * dealt) return 0;
+  prm.chunked = 1;
+  prm.pairs_per_head = prm.q_tiles / 2;
+  prm.singles_per_head = prm.q_tiles % 2;
+  prm.magic_pairs = div_magic(prm.pairs_per_head);
+  prm.magic_singles = div_magic(prm.singles_per_head);
+  prm.pair_items = static_cast<int>(pairs);
+  prm.single_items = static_cast<int>(singles);
+  prm.cost_total = cost;
+  prm.cost_base = cost / grid;
+  prm.cost_rem = static_cast<int>(cost % grid);
+  prm.magic_kv_tiles = div_magic(prm.kv_tiles);
+  prm.test_flags = a->test_flags;
+  prm.ws_partial = static_cast<float*>(a->workspace);
+  prm.ws_counts = reinterpret_cast<uint32_t*>(static_cast<char*>(a->workspace) + workspace_flags_offset(sms));
+  return static_cast<unsigned>(grid);
+}
+
+// The work plan of a call on a device with `sms` SMs: fills the plan fields of `prm`, returns the grid size.
+unsigned plan_work(AttnParams& prm, const B200AttnArgs* a, int sms) {
+  const long long heads_total = static_cast<long long>(a->batch) * a->heads;
+  double dealt_span = 0;
+  unsigned grid = plan_split(prm, heads_total, sms, &dealt_span);
+  if (const unsigned chunk_grid = plan_chunks(prm, a, heads_total, sms, dealt_span)) grid = chunk_grid;
+  return grid;
+}
+
+template <typename T, int BIAS, bool SHORT, bool SPLIT>
+int launch(const AttnParams& planned, unsigned grid, DeviceState& dev, const CUtensorMap& mq, const CUtensorMap& mk,
+           const CUtensorMap& mv, const CUtensorMap& mo, cudaStream_t stream) {
+  auto kernel = attn_fwd_kernel<T, BIAS, SHORT, SPLIT>;
   constexpr int smem = static_cast<int>(sizeof(AttnSmem)) + 1024;
-  constexpr int form = (BIAS * 2 + (std::is_same<T, __half>::value ? 0 : 1)) * 2 + (SHORT ? 1 : 0);
+  constexpr int form = (BIAS * 2 + (std::is_same<T, __half>::value ? 0 : 1)) * 3 + (SHORT ? 1 : SPLIT ? 2 : 0);
   static_assert(form < kKernelForms, "kernel form index");
   if (!dev.opted_in[form].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -291,8 +348,6 @@ int launch(const B200AttnArgs* a, const AttnParams& prm, DeviceState& dev, const
     dev.opted_in[form].store(true, std::memory_order_release);
   }
   // Persistent CTAs: one per SM (shared memory and tensor memory allow no more), fewer when there is less work.
-  AttnParams planned = prm;
-  const unsigned grid = plan_split(planned, static_cast<long long>(a->batch) * a->heads, dev.sms);
   // Programmatic stream serialisation: the CTAs of this grid may be scheduled while the previous kernel of the stream
   // drains; the kernel waits for that kernel's completion itself (grid_dependency_wait) before it touches global
   // memory, so its set-up (barriers, tensor memory, descriptor prefetch) and the launch latency hide behind the
@@ -314,14 +369,16 @@ int launch(const B200AttnArgs* a, const AttnParams& prm, DeviceState& dev, const
 }
 
 // The short schedule exists for every bias form but the 64-wide one (its key counts are multiples of 64, where the
-// long schedule loses nothing worth a second set of kernels).
+// long schedule loses nothing worth a second set of kernels); the key-split form only for the long schedule (a
+// sequence of at most two key tiles is never split).
 template <typename T, int BIAS>
-int launch_sched(bool short_sched, const B200AttnArgs* a, const AttnParams& prm, DeviceState& dev, const CUtensorMap& mq,
+int launch_sched(bool short_sched, const AttnParams& planned, unsigned grid, DeviceState& dev, const CUtensorMap& mq,
                  const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, cudaStream_t stream) {
+  if (planned.chunked) return launch<T, BIAS, false, true>(planned, grid, dev, mq, mk, mv, mo, stream);
   if constexpr (BIAS != kBiasDecomposed64) {
-    if (short_sched) return launch<T, BIAS, true>(a, prm, dev, mq, mk, mv, mo, stream);
+    if (short_sched) return launch<T, BIAS, true, false>(planned, grid, dev, mq, mk, mv, mo, stream);
   }
-  return launch<T, BIAS, false>(a, prm, dev, mq, mk, mv, mo, stream);
+  return launch<T, BIAS, false, false>(planned, grid, dev, mq, mk, mv, mo, stream);
 }
 
 }  // namespace
@@ -393,24 +450,70 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
 #ifdef B200_TRACE
   prm.trace = g_trace_buffer;
 #endif
+  const unsigned grid = plan_work(prm, a, dev->sms);
   const bool f16 = a->dtype == B200_ATTN_F16;
+  const bool short_sched = sched == B200_ATTN_SCHED_SHORT;
   switch (bias_mode) {
     case kBiasNone:
-      return f16 ? launch_sched<__half, kBiasNone>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream)
-                 : launch_sched<__nv_bfloat16, kBiasNone>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream);
+      return f16 ? launch_sched<__half, kBiasNone>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream)
+                 : launch_sched<__nv_bfloat16, kBiasNone>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream);
     case kBiasDense:
-      return f16 ? launch_sched<__half, kBiasDense>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream)
-                 : launch_sched<__nv_bfloat16, kBiasDense>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream);
+      return f16 ? launch_sched<__half, kBiasDense>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream)
+                 : launch_sched<__nv_bfloat16, kBiasDense>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream);
     case kBiasDecomposed64:
-      return f16 ? launch_sched<__half, kBiasDecomposed64>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream)
-                 : launch_sched<__nv_bfloat16, kBiasDecomposed64>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream);
+      return f16 ? launch_sched<__half, kBiasDecomposed64>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream)
+                 : launch_sched<__nv_bfloat16, kBiasDecomposed64>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream);
     case kBiasDecomposed14:
-      return f16 ? launch_sched<__half, kBiasDecomposed14>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream)
-                 : launch_sched<__nv_bfloat16, kBiasDecomposed14>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream);
+      return f16 ? launch_sched<__half, kBiasDecomposed14>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream)
+                 : launch_sched<__nv_bfloat16, kBiasDecomposed14>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream);
     default:
-      return f16 ? launch_sched<__half, kBiasDecomposed>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream)
-                 : launch_sched<__nv_bfloat16, kBiasDecomposed>(sched == B200_ATTN_SCHED_SHORT, a, prm, *dev, mq, mk, mv, mo, stream);
+      return f16 ? launch_sched<__half, kBiasDecomposed>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream)
+                 : launch_sched<__nv_bfloat16, kBiasDecomposed>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream);
   }
+}
+
+int b200_attn_plan(const B200AttnArgs* a, int32_t sms, int32_t cta, int32_t* grid_out, int32_t* items_out,
+                   int32_t max_items, int32_t* n_items_out, int32_t* later_parts_out) {
+  int bias_mode = 0, sched = 0;
+  int rc = validate(a, &bias_mode, &sched);
+  if (rc != B200_ATTN_OK) return rc;
+  if (sms < 1 || grid_out == nullptr || n_items_out == nullptr || later_parts_out == nullptr || (items_out == nullptr && max_items > 0))
+    return fail(B200_ATTN_BAD_CONFIG, "b200_attn_plan: sms must be positive and the output pointers not NULL");
+  AttnParams prm;
+  std::memset(&prm, 0, sizeof(prm));
+  prm.batch = a->batch;
+  prm.heads = a->heads;
+  prm.q_tokens = a->q_tokens;
+  prm.kv_tokens = a->kv_tokens;
+  prm.q_tiles = (a->q_tokens + kTileRows - 1) / kTileRows;
+  prm.kv_tiles = (a->kv_tokens + kTileRows - 1) / kTileRows;
+  prm.magic_heads = div_magic(a->heads);
+  B200AttnArgs with_ws = *a;
+  if (with_ws.workspace != nullptr && static_cast<size_t>(with_ws.workspace_bytes) < workspace_bytes_for(sms)) {
+    with_ws.workspace = nullptr;  // as b200_attn_fwd: too small a workspace is not used
+    with_ws.workspace_bytes = 0;
+  }
+  const int grid = static_cast<int>(plan_work(prm, &with_ws, sms));
+  *grid_out = grid;
+  if (cta < 0 || cta >= grid) return fail(B200_ATTN_BAD_CONFIG, "b200_attn_plan: cta %d outside the grid of %d", cta, grid);
+  const CtaWork cw = cta_work(prm, cta, grid);
+  const int n = cw.pairs + cw.singles;
+  *n_items_out = n;
+  *later_parts_out = cw.last_parts;
+  for (int it = 0; it < n && it < max_items; ++it) {
+    const WorkItem w = prm.chunked ? decode_item<true>(prm, cw, it) : decode_item<false>(prm, cw, it);
+    int32_t* o = items_out + 7 * it;
+    o[0] = w.b; o[1] = w.h; o[2] = w.q_row0; o[3] = w.n_tiles; o[4] = w.ja; o[5] = w.jb; o[6] = w.kind;
+  }
+  return B200_ATTN_OK;
+}
+
+int b200_attn_workspace_size(int64_t* bytes) {
+  if (bytes == nullptr) return fail(B200_ATTN_BAD_CONFIG, "bytes is NULL");
+  DeviceState* dev = nullptr;
+  if (const int rc = device_state(&dev)) return rc;
+  *bytes = static_cast<int64_t>(workspace_bytes_for(dev->sms));
+  return B200_ATTN_OK;
 }
 
 int b200_attn_status(uint32_t* status) {
@@ -430,6 +533,14 @@ int b200_attn_status(uint32_t* status) {
 
 #ifdef B200_TRACE
 void b200_attn_debug_set_trace(void* device_buffer) { g_trace_buffer = static_cast<long long*>(device_buffer); }
+int b200_attn_debug_timeouts(unsigned int* out /* [256][4] */) {
+  unsigned int n = 0, zero = 0;
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(&n, b200::g_dbg_count, sizeof(n));
+  cudaMemcpyFromSymbol(out, b200::g_dbg, sizeof(unsigned int) * 256 * 4);
+  cudaMemcpyToSymbol(b200::g_dbg_count, &zero, sizeof(zero));
+  return static_cast<int>(n);
+}
 #endif
 
 int b200_attn_selftest_wait_limit(uint32_t limit_us, void* stream_ptr) {
@@ -446,6 +557,11 @@ int b200_attn_selftest_wait_limit(uint32_t limit_us, void* stream_ptr) {
 
 const char* b200_attn_last_error(void) { return tl_error; }
 
-const char* b200_attn_version(void) { return "b200attn 0.1 (sm_100a, tcgen05 + TMA)"; }
+// The build passes the digest of the sources (fastforks_b200/_lib.py: source_hash); the loader compares it with the
+// sources beside the binary and refuses a binary of other sources.
+#ifndef B200_SOURCE_HASH
+#define B200_SOURCE_HASH "0000000000000000"
+#endif
+const char* b200_attn_version(void) { return "b200attn 0.2 (sm_100a, tcgen05 + TMA) b200attn-src:" B200_SOURCE_HASH; }
 
 }  // extern "C"

@@ -96,8 +96,23 @@ typedef struct B200AttnArgs {
   int64_t rel_h_stride[3];
   int64_t rel_w_stride[3];
 
-  int32_t schedule; /* B200_ATTN_SCHED_* */
-  int32_t reserved;
+  int32_t schedule;   /* B200_ATTN_SCHED_* */
+  int32_t test_flags; /* 0.  For tests: 1 makes every merge of a split launch (see `workspace`) take its general,
+                       * slower route, which otherwise only runs when parts complete in an unusual order. */
+
+  /* Optional scratch memory for long sequences: `workspace_bytes` bytes of device memory, 256-byte aligned, at
+   * least b200_attn_workspace_size() of them, ZEROED once when it is allocated and then left to the library (the
+   * kernel leaves it ready for the next launch).  With it, sequences of more than two key tiles are split along the
+   * keys where whole query tiles are too coarse to keep every SM busy to the end of the launch (1370 tokens x 48 heads is
+   * 3.6 query tiles per SM): the CTAs that share a tile leave partial results (unnormalised output, row maxima, row
+   * sums) there and are counted; the CTA with the tile's first keys folds them in when they are all there, as they
+   * are as a rule, else whichever part is counted last does.
+   * No CTA waits for another, so grids of several streams may share the GPU in any way.  NULL / 0 = never split (every call then works as it does without
+   * scratch memory, only slower where the split would have paid).  Launches that may run at the same time (other
+   * streams) need workspaces of their own; the reference keys its workspaces by (device, stream) the same way
+   * (src/fastforks/_optimize/ops.py:248-296).  After a launch that b200_attn_status reports as failed, zero it again. */
+  void* workspace;
+  int64_t workspace_bytes;
 } B200AttnArgs;
 
 /*
@@ -119,6 +134,27 @@ int b200_attn_fwd(const B200AttnArgs* args, void* stream);
  * only inspected for alignment.  Counterpart of `check_flash64` (fastbb/__init__.py:51-67).
  */
 int b200_attn_query(const B200AttnArgs* args, int32_t* schedule);
+
+/*
+ * Describes, without launching and without a GPU, the work the kernel's CTA number `cta` would do for `args` on a
+ * device with `sms` SMs (148 on a B200): the grid size in *grid, the CTA's item count in *n_items, up to `max_items`
+ * items as 7 integers each in `items` - batch, head, first query row, query tiles (1 or 2), first key tile, end key
+ * tile, kind (0 whole item, 1 a part whose result goes to the workspace, 2 the part that merges the later ones) -
+ * and in *later_parts how many following CTAs hold later parts of its last item.  The plan is computed by the very
+ * functions the kernel runs, so tests can check on a CPU that every (query tile, key tile) of a problem is covered
+ * exactly once.  `args->workspace` only matters as NULL / not NULL (with a workspace long sequences may be split).
+ * The reference has no counterpart: its grid is (query tiles, batch * heads), fastbb/__init__.py:130-135.
+ */
+int b200_attn_plan(const B200AttnArgs* args, int32_t sms, int32_t cta, int32_t* grid, int32_t* items, int32_t max_items,
+                   int32_t* n_items, int32_t* later_parts);
+
+/*
+ * Stores in *bytes the workspace size that is enough for any call on the current device (it depends on the
+ * device's SM count only: four partial tiles of 33 KB and two counters per SM, about 20 MB on a B200).
+ * The reference sizes the workspace of its GEMM library with a constant and keeps one per (device, stream)
+ * (`_PW_WS`, src/fastforks/_optimize/ops.py:248-296); a caller of this library should do the same.
+ */
+int b200_attn_workspace_size(int64_t* bytes);
 
 /*
  * Reads and clears the device-side error word of the current device (synchronises that device).

@@ -44,8 +44,12 @@ def oracle_of_packed(qkv: torch.Tensor, scale: float, **kw: object) -> np.ndarra
 
 
 def test_library_is_the_cuda_build() -> None:
+    """The loaded binary is the sm_100a build of the sources beside it: its version string carries their digest."""
+    from fastforks_b200 import _lib
+
     assert ff.resolve_mode("kernels") == "kernels"
     assert "sm_100a" in ff.version()
+    assert ff.version().endswith(f"b200attn-src:{_lib.source_hash()}")
 
 
 @pytest.mark.parametrize("name", ["dinov2_n97", "dinov2_n257_peaky", "timm_n197"])
@@ -243,6 +247,75 @@ def test_full_size_configs_by_properties(b: int, h: int, n: int, dtype: str) -> 
     assert_close(got[:: max(1, b // 2), :, :: max(1, h // 2)].float().cpu().numpy(), ref, unit_scale=True)
 
 
+def oracle_of_heads(qkv: torch.Tensor, picks: list[tuple[int, int]], scale: float, rel: tuple | None = None) -> np.ndarray:
+    """Oracle output `[len(picks), N, 64]` for the chosen (batch, head) pairs of a packed `[B, N, 3, H, 64]` tensor,
+    one head at a time (a dense 4096 x 4096 bias is 64 MB per head)."""
+    rows = []
+    for b, h in picks:
+        q, k, v = (qkv[b, :, i, h].float().cpu().numpy()[None, None] for i in range(3))
+        bias = None
+        if rel is not None:
+            bias = ao.decomposed_bias(rel[0][b, h].float().cpu().numpy()[None, None], rel[1][b, h].float().cpu().numpy()[None, None])
+        rows.append(ao.attention(q, k, v, scale, bias)[0, 0])
+    return np.stack(rows)
+
+
+@pytest.mark.parametrize(
+    ("b", "h", "n", "dtype", "stride"),
+    [(32, 24, 1370, "bf16", 97), (256, 12, 197, "fp16", 61), (8, 6, 1370, "fp16", 5), (4, 16, 1370, "bf16", 7)],
+)
+def test_benchmarked_shapes_against_the_oracle(b: int, h: int, n: int, dtype: str, stride: int) -> None:
+    """Every shape a benchmark number is quoted on, launched at full size (the work split and the grid are the
+    benchmark's) and compared with the oracle on a strided sample of (batch, head) pairs that always contains the
+    first and the last head. A NaN canary in the output shows any row the launch failed to write."""
+    qkv = packed_qkv(b, n, h, DTYPES[dtype], 1.0, seed=b * 1000 + n)
+    q, k, v = qkv.unbind(2)
+    out = torch.full((b, n, h, 64), float("nan"), dtype=DTYPES[dtype], device="cuda")
+    ff.attention(q, k, v, scale=0.125, layout="bnhd", out=out)
+    assert bool(torch.isfinite(out).all())
+    ids = sorted({*range(0, b * h, stride), b * h - 1})
+    picks = [(i // h, i % h) for i in ids]
+    ref = oracle_of_heads(qkv, picks, 0.125)
+    got = np.stack([out[bi, :, hi].float().cpu().numpy() for bi, hi in picks])
+    assert_close(got, ref, unit_scale=True, what=f"[{b},{h},{n},64] {dtype}, {len(picks)} heads")
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_sam_global_grid_with_decomposed_bias_all_heads(dtype: str) -> None:
+    """SAM-B's global layers at full size, `[1, 12, 4096, 64]` with `rel_h`, `rel_w` `[1, 12, 4096, 64]`: all twelve
+    heads in one launch (384 query tiles on 148 CTAs, the benchmark's work split), every head against the oracle."""
+    dt = DTYPES[dtype]
+    b, h, n = 1, 12, 4096
+    qkv = packed_qkv(b, n, h, dt, 1.0, seed=4096)
+    gen = torch.Generator().manual_seed(64)
+    rel = tuple(torch.randn(b, h, n, 64, generator=gen).to(dt).cuda() for _ in range(2))
+    q, k, v = qkv.unbind(2)
+    out = torch.full((b, n, h, 64), float("nan"), dtype=dt, device="cuda")
+    ff.attention(q, k, v, scale=0.125, layout="bnhd", out=out, rel=rel)
+    assert bool(torch.isfinite(out).all())
+    picks = [(0, i) for i in range(h)]
+    ref = oracle_of_heads(qkv, picks, 0.125, rel=rel)
+    got = np.stack([out[0, :, i].float().cpu().numpy() for i in range(h)])
+    assert_close(got, ref, unit_scale=True, what=f"SAM global grid {dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_sam_windows_with_decomposed_bias_full_size(dtype: str) -> None:
+    """SAM-B's windowed layers at full size: 25 windows x 12 heads of 14 x 14 tokens with `rel_h`, `rel_w`
+    `[25, 12, 196, 14]`, packed-qkv views in, every (window, head) against the oracle."""
+    dt = DTYPES[dtype]
+    b, h, n = 25, 12, 196
+    qkv = packed_qkv(b, n, h, dt, 1.0, seed=196)
+    gen = torch.Generator().manual_seed(14)
+    rel = tuple(torch.randn(b, h, n, 14, generator=gen).to(dt).cuda() for _ in range(2))
+    q, k, v = qkv.unbind(2)
+    out = torch.full((b, n, h, 64), float("nan"), dtype=dt, device="cuda")
+    ff.attention(q, k, v, scale=0.125, layout="bnhd", out=out, rel=rel)
+    bias = ao.decomposed_bias(rel[0].float().cpu().numpy(), rel[1].float().cpu().numpy())
+    ref = oracle_of_packed(qkv, 0.125, bias=bias)
+    assert_close(out.float().cpu().numpy(), ref, unit_scale=True, what=f"SAM windows {dtype}")
+
+
 def test_two_streams_equal_one_stream() -> None:
     """Launches on two torch streams give the same bits as on one (the reference checks its kernels the same way,
     tests/test_threads.py:58-332)."""
@@ -261,19 +334,92 @@ def test_two_streams_equal_one_stream() -> None:
 
 
 def test_cuda_graph_replay_equals_eager() -> None:
-    """The launch is capturable (families capture whole forwards, src/fastforks/shared/cuda_graphs.py:1-17)."""
+    """The launch is capturable (families capture whole forwards, src/fastforks/shared/cuda_graphs.py:1-17). The
+    workspace of the capture stream is reserved before the capture, so the captured launch may split along the keys
+    like the eager one; replays with new contents in the same buffers must follow them (the kernel leaves the
+    workspace ready for its next launch, whatever launched it)."""
     qkv = packed_qkv(2, 1370, 6, torch.float16, 1.0, 22)
     q, k, v = qkv.unbind(2)
     out = torch.empty(2, 1370, 6, 64, dtype=torch.float16, device="cuda")
     eager = ff.attention(q, k, v, layout="bnhd").clone()
     torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ff.reserve_workspace()
     graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
+    with torch.cuda.graph(graph, stream=stream):
         ff.attention(q, k, v, layout="bnhd", out=out)
     out.zero_()
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(out, eager)
+    for seed in (23, 24):
+        qkv.copy_(packed_qkv(2, 1370, 6, torch.float16, 1.0, seed))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert_close(out.float().cpu().numpy(), oracle_of_packed(qkv, 0.125), unit_scale=True, what=f"replay seed {seed}")
+
+
+def test_capture_without_a_reserved_workspace_runs_unsplit() -> None:
+    """Nothing is allocated during a capture: a capture on a stream that never reserved a workspace launches the
+    unsplit form, which must give the oracle's result too."""
+    qkv = packed_qkv(1, 1370, 6, torch.float16, 1.0, 25)
+    q, k, v = qkv.unbind(2)
+    out = torch.empty(1, 1370, 6, 64, dtype=torch.float16, device="cuda")
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):  # torch captures on a side stream of its own: no workspace there
+        ff.attention(q, k, v, layout="bnhd", out=out)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert_close(out.float().cpu().numpy(), oracle_of_packed(qkv, 0.125), unit_scale=True)
+
+
+SPLIT_SHAPES = [(1, 6, 1370, None), (8, 6, 1370, None), (1, 12, 4096, None), (3, 7, 900, None), (1, 2, 300, 1000), (1, 1, 129, 20000), (2, 16, 1370, None)]
+
+
+@pytest.mark.parametrize(("b", "h", "n", "nk"), SPLIT_SHAPES)
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_key_split_launches_match_the_oracle_on_both_merge_routes(b: int, h: int, n: int, nk: int | None, dtype: str) -> None:
+    """Long sequences whose query tiles level badly over 148 SMs are cut along the keys (`workspace` in
+    include/b200_attn.h). Runs of two to twenty key tiles per CTA, items cut into up to five parts: the result must
+    be the oracle's, on the usual route (the owner of a cut item folds the later parts in) and on the general one
+    (a store warp folds them), with the same bits on both and on every repeat (the workspace is left ready)."""
+    dt = DTYPES[dtype]
+    nk = n if nk is None else nk
+    gen = torch.Generator().manual_seed(n + nk)
+    q = torch.randn(b, n, h, 64, generator=gen).to(dt).cuda()
+    k, v = (torch.randn(b, nk, h, 64, generator=gen).to(dt).cuda() for _ in range(2))
+    ref = ao.attention(*(t.float().cpu().numpy().transpose(0, 2, 1, 3) for t in (q, k, v)), 0.125).transpose(0, 2, 1, 3)
+    outs = []
+    for general in (False, True, False, True):
+        out = torch.full((b, n, h, 64), float("nan"), dtype=dt, device="cuda")
+        ff.attention(q, k, v, scale=0.125, layout="bnhd", out=out, _general_merge=general)
+        assert_close(out.float().cpu().numpy(), ref, unit_scale=True, what=f"[{b},{h},{n}x{nk}] {dtype} general={general}")
+        outs.append(out)
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+
+
+def test_key_split_with_decomposed_and_dense_bias() -> None:
+    """The bias forms walk absolute key positions: a part that begins in the middle of the keys must read the
+    right columns of a dense bias and the right rows of the decomposed tables (SAM's 64-wide form fetches `rel_h`
+    in groups of four key tiles)."""
+    gen = torch.Generator().manual_seed(77)
+    b, h, n = 1, 3, 2048
+    q, k, v = (torch.randn(b, n, h, 64, generator=gen).half().cuda() for _ in range(3))
+    rel = tuple(torch.randn(b, h, n, 64 if i else 32, generator=gen).half().cuda() for i in range(2))
+    args = [t.float().cpu().numpy().transpose(0, 2, 1, 3) for t in (q, k, v)]
+    ref = ao.attention(*args, 0.125, ao.decomposed_bias(rel[0].float().cpu().numpy(), rel[1].float().cpu().numpy()))
+    for general in (False, True):
+        got = ff.attention(q, k, v, scale=0.125, layout="bnhd", rel=rel, _general_merge=general)
+        assert_close(got.float().cpu().numpy().transpose(0, 2, 1, 3), ref, unit_scale=True, what=f"rel 32x64 general={general}")
+    n = 1000
+    q, k, v = (torch.randn(b, n, h, 64, generator=gen).half().cuda() for _ in range(3))
+    bias = torch.randn(1, h, n, n, generator=gen).half()
+    args = [t.float().cpu().numpy().transpose(0, 2, 1, 3) for t in (q, k, v)]
+    ref = ao.attention(*args, 0.125, bias.float().numpy())
+    got = ff.attention(q, k, v, scale=0.125, layout="bnhd", bias=bias.cuda())
+    assert_close(got.float().cpu().numpy().transpose(0, 2, 1, 3), ref, unit_scale=True, what="dense bias, split")
 
 
 def test_contract_violations_raise_before_launch() -> None:
