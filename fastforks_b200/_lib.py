@@ -37,7 +37,7 @@ NVCC_FLAGS = (
 
 # Every symbol include/b200_attn.h declares.
 EXPORTS = (
-    "b200_attn_fwd", "b200_attn_query", "b200_attn_plan", "b200_attn_workspace_size", "b200_attn_status",
+    "b200_attn_fwd", "b200_attn_fwd_static", "b200_attn_query", "b200_attn_plan", "b200_attn_workspace_size", "b200_attn_status",
     "b200_attn_selftest_wait_limit", "b200_attn_last_error", "b200_attn_version",
 )  # fmt: skip
 
@@ -157,6 +157,8 @@ def library() -> ctypes.CDLL:
         raise KernelUnavailableError(LIBRARY, f"{SHARED_OBJECT.name} lacks the symbols {missing}")
     lib.b200_attn_fwd.argtypes = (ctypes.POINTER(B200AttnArgs), ctypes.c_void_p)
     lib.b200_attn_fwd.restype = ctypes.c_int
+    lib.b200_attn_fwd_static.argtypes = (ctypes.POINTER(B200AttnArgs), ctypes.c_void_p)
+    lib.b200_attn_fwd_static.restype = ctypes.c_int
     lib.b200_attn_query.argtypes = (ctypes.POINTER(B200AttnArgs), ctypes.POINTER(ctypes.c_int32))
     lib.b200_attn_query.restype = ctypes.c_int
     i32p = ctypes.POINTER(ctypes.c_int32)

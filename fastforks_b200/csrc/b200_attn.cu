@@ -326,6 +326,18 @@ unsigned plan_chunks(AttnParams& prm, const B200AttnArgs* a, long long heads_tot
   return static_cast<unsigned>(grid);
 }
 
+// Scratch memory of b200_attn_fwd_static: a workspace for devices of up to kStaticMaxSms SMs (a B200 has 148) that
+// lives in the module itself, 21.6 MB on every GPU that loads the library, until the process ends.
+constexpr int kStaticMaxSms = 160;
+constexpr size_t kStaticWorkspaceBytes =
+    (static_cast<size_t>(kStaticMaxSms) * kPartialBytes + static_cast<size_t>(kStaticMaxSms) * 2 * sizeof(uint32_t) + 255) & ~size_t(255);
+static __device__ __align__(256) unsigned char g_static_workspace[kStaticWorkspaceBytes];
+struct StaticScratch {
+  std::atomic<bool> ready{false};
+  void* ptr = nullptr;  // device address of g_static_workspace on this device
+};
+StaticScratch g_static_scratch[kMaxDevices];
+
 // The work plan of a call on a device with `sms` SMs: fills the plan fields of `prm`, returns the grid size.
 unsigned plan_work(AttnParams& prm, const B200AttnArgs* a, int sms) {
   const long long heads_total = static_cast<long long>(a->batch) * a->heads;
@@ -514,6 +526,42 @@ int b200_attn_workspace_size(int64_t* bytes) {
   if (const int rc = device_state(&dev)) return rc;
   *bytes = static_cast<int64_t>(workspace_bytes_for(dev->sms));
   return B200_ATTN_OK;
+}
+
+int b200_attn_fwd_static(const B200AttnArgs* a, void* stream_ptr) {
+  if (a == nullptr) return fail(B200_ATTN_BAD_CONFIG, "args is NULL");
+  DeviceState* dev = nullptr;
+  if (const int rc = device_state(&dev)) return rc;
+  if (dev->sms > kStaticMaxSms)
+    return fail(B200_ATTN_UNSUPPORTED,
+                "b200_attn_fwd_static: this device has %d SMs, the built-in scratch array holds the partial results of "
+                "at most %d; use b200_attn_fwd with a workspace of b200_attn_workspace_size() bytes",
+                dev->sms, kStaticMaxSms);
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  // Set-up, once per device and with that device current: in host code the array's name is only a handle for the
+  // runtime, the address a kernel can use has to be asked for.
+  StaticScratch& scratch = g_static_scratch[device];
+  if (!scratch.ready.load(std::memory_order_acquire)) {
+    std::lock_guard<std::mutex> lock(g_devices_mutex);
+    if (!scratch.ready.load(std::memory_order_relaxed)) {
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_static_workspace);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(built-in scratch array)");
+      scratch.ptr = ptr;
+      scratch.ready.store(true, std::memory_order_release);
+    }
+  }
+  B200AttnArgs with_scratch = *a;
+  with_scratch.workspace = scratch.ptr;
+  with_scratch.workspace_bytes = static_cast<int64_t>(workspace_bytes_for(dev->sms));
+  // The array keeps what the last call left. The partial results are written before they are read; the counters
+  // must start at zero, and a call that was cut short may have left some raised: clear them, in stream order.
+  e = cudaMemsetAsync(static_cast<char*>(scratch.ptr) + workspace_flags_offset(dev->sms), 0,
+                      static_cast<size_t>(dev->sms) * 2 * sizeof(uint32_t), static_cast<cudaStream_t>(stream_ptr));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(counters of the built-in scratch array)");
+  return b200_attn_fwd(&with_scratch, stream_ptr);
 }
 
 int b200_attn_status(uint32_t* status) {

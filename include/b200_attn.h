@@ -128,6 +128,28 @@ typedef struct B200AttnArgs {
 int b200_attn_fwd(const B200AttnArgs* args, void* stream);
 
 /*
+ * b200_attn_fwd for callers that have no device memory to give: the same call, but long sequences are split with
+ * scratch memory that is built into the library (`args->workspace` and `workspace_bytes` are ignored) and nothing
+ * is allocated, by this call or on its behalf.  It is meant for hosts that cannot call cudaMalloc where they call
+ * attention: a serving loop that handed all device memory to a pool of its own at start-up, a pipeline that must
+ * not take the device-wide synchronisation an allocation or a free implies, a plain C or ctypes caller that only
+ * holds the pointers of its inputs and outputs.  It has no counterpart in the reference, whose callers always
+ * have torch's allocator at hand (src/fastforks/_optimize/ops.py:248-296).
+ *
+ * The price and the limits:
+ *   - the scratch array is sized for devices of up to 160 SMs (a B200 has 148): 21.6 MB, held on every GPU that
+ *     loads the library until the process ends.  On a device with more SMs the call returns
+ *     B200_ATTN_UNSUPPORTED and the message says so; use b200_attn_fwd with a workspace there;
+ *   - there is ONE array per device and every call uses it: calls that may overlap on the GPU (two streams, two
+ *     threads) race on it and give wrong results.  Calls on one stream are safe.  The array keeps the last call's
+ *     contents; the call clears, in stream order, the counters that must start from zero;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress, once per device, with
+ *     that device current).  Make that first call before any stream capture begins.
+ * Return codes, argument checks, stream and status-word behaviour are those of b200_attn_fwd, and so is the result.
+ */
+int b200_attn_fwd_static(const B200AttnArgs* args, void* stream);
+
+/*
  * Reports whether `args` describes a call the library can run, without launching: returns the code
  * `b200_attn_fwd` would return from its argument checks, and stores the schedule it would pick
  * (B200_ATTN_SCHED_LONG / SHORT) in *schedule when that pointer is not NULL.  Pointers in `args` are
