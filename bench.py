@@ -15,6 +15,9 @@ The JSON line carries, besides the contract's keys:
   e2e           the same metric through the public operator with HOST buffers: pinned-memory qkv copied to the
                 device, attention, output copied back, every step
   regimes       the other benchmark shapes, device-timed: long-sequence TFLOP/s and short-sequence HBM GB/s
+  model         ViT-L/14 518 px encoder around the kernel: images/s device-timed and end to end from host images
+  partition     ViT-g/14 518 px, 256 images split image-wise over the ranks (strong scaling), gathered to rank 0 after
+                the timed region
 
 `--impl reference` times the reference's own CPU implementation of the path (see `oracle/portable_attention.py`)
 on the same configuration and metric.
@@ -58,10 +61,11 @@ CASES = {
     "vit-b16-b256": (256, 12, 197, "fp16", None),
     "vit-b16-b1": (1, 12, 197, "fp16", None),
 }
-# DRAM bytes of one launch of the headline kernel ([8,6,1370,64] fp16), dram__bytes_read.sum + dram__bytes_write.sum
-# of the capture summarised in profiles/attn_fwd_dinov2-vits14.md: q, k, v are read once (25.3 MB), the 8.4 MB
-# output is still in L2 when the kernel ends.
+# DRAM bytes of one launch of the headline kernel ([8,6,1370,64] fp16): dram__bytes_read.sum + dram__bytes_write.sum
+# of one profiler capture of `python bench.py --case dinov2-vits14` (q, k, v are read once, 25.3 MB; the 8.4 MB output
+# is still in L2 when the kernel ends). A profiler figure, not something this run measures: the line says so.
 TRAFFIC_BYTES_PER_LAUNCH = 25.3e6
+MIN_TIMED_SECONDS = 0.5  # the K-step region is repeated until this much device time has been measured
 
 
 def attention_flops(b: int, h: int, n: int, nk: int | None = None) -> float:
@@ -140,28 +144,39 @@ class ClockSampler:
         return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
 
 
-def cpu_reference_tflops(layers: int, threads: int, *, warm: int = 2, runs: int = 5) -> tuple[float, float, str]:
-    """The reference's portable arithmetic on the host: fp32 SDPA of `layers` layers of the workload shape.
+class CpuReference:
+    """The reference's portable arithmetic on the host: fp32 SDPA of `layers` layers of the workload shape, on
+    buffers allocated (and touched) once."""
 
-    Returns (TFLOP/s, seconds per pass, description of the sample)."""
-    import torch
+    def __init__(self, layers: int, threads: int) -> None:
+        import torch
 
-    from oracle.portable_attention import portable_attention
+        from oracle.portable_attention import portable_attention
 
-    torch.set_num_threads(threads)
-    b, h, n = WORKLOAD["batch"], WORKLOAD["heads"], WORKLOAD["tokens"]
-    gen = torch.Generator().manual_seed(0)
-    qkv = [torch.randn(3, b, h, n, HEAD_DIM, generator=gen) for _ in range(layers)]
-    times = []
-    for i in range(warm + runs):
+        torch.set_num_threads(threads)
+        self.run = portable_attention
+        self.layers, self.threads = layers, threads
+        b, h, n = WORKLOAD["batch"], WORKLOAD["heads"], WORKLOAD["tokens"]
+        gen = torch.Generator().manual_seed(0)
+        self.qkv = [torch.randn(3, b, h, n, HEAD_DIM, generator=gen) for _ in range(layers)]
+        self.flops = attention_flops(b, h, n) * layers
+        self.sample = f"{layers} of {WORKLOAD['layers']} layers of [{b},{h},{n},{HEAD_DIM}] fp32 per pass"
+
+    def one_pass(self) -> float:
+        """Seconds of one pass over the sample."""
         t0 = time.perf_counter()
-        for x in qkv:
-            portable_attention(x[0], x[1], x[2])
-        if i >= warm:
-            times.append(time.perf_counter() - t0)
-    sec = statistics.median(times)
-    sample = f"{layers} of {WORKLOAD['layers']} layers of [{b},{h},{n},{HEAD_DIM}] fp32, median of {runs} passes after {warm} warm-ups"
-    return attention_flops(b, h, n) * layers / sec / 1e12, sec, sample
+        for x in self.qkv:
+            self.run(x[0], x[1], x[2])
+        return time.perf_counter() - t0
+
+
+def cpu_reference_tflops(layers: int, threads: int, *, warm: int = 2, runs: int = 5) -> tuple[float, float, str]:
+    """(TFLOP/s, seconds per pass, description of the sample): median of `runs` passes after `warm` warm-ups."""
+    ref = CpuReference(layers, threads)
+    for _ in range(warm):
+        ref.one_pass()
+    sec = statistics.median(ref.one_pass() for _ in range(runs))
+    return ref.flops / sec / 1e12, sec, f"{ref.sample}, median of {runs} passes after {warm} warm-ups"
 
 
 def base_line(args: argparse.Namespace) -> dict:
@@ -193,12 +208,13 @@ def run_reference(args: argparse.Namespace) -> None:
         return
     threads = os.cpu_count() or 1
     layers = 2  # bounded sample of the 12-layer step; throughput is per FLOP, so the sample needs no scaling
-    for _ in range(max(0, args.warmup)):
-        cpu_reference_tflops(layers, threads, warm=0, runs=1)
+    ref = CpuReference(layers, threads)  # buffers are allocated and first touched here, outside every timed pass
+    for _ in range(max(1, args.warmup)):
+        ref.one_pass()
     t0 = time.perf_counter()
-    values = [cpu_reference_tflops(layers, threads, warm=0, runs=1) for _ in range(max(1, args.steps))]
+    passes = [ref.one_pass() for _ in range(max(1, args.steps))]
     elapsed = time.perf_counter() - t0
-    tflops = statistics.median(v[0] for v in values)
+    tflops = ref.flops / statistics.median(passes) / 1e12
     line = base_line(args)
     line.update(
         impl="reference",
@@ -210,8 +226,8 @@ def run_reference(args: argparse.Namespace) -> None:
             "unit": "TFLOP/s",
             "cores": threads,
             "kind": "port",
-            "sample": f"{layers} of {WORKLOAD['layers']} layers per step: fp32 torch scaled_dot_product_attention on the host, "
-            "the call the reference's portable backend makes",
+            "sample": f"{layers} of {WORKLOAD['layers']} layers per step, same buffers every step, median step: fp32 torch "
+            "scaled_dot_product_attention on the host, the call the reference's portable backend makes",
         },
         e2e={"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         gpu_launches=0,
@@ -219,14 +235,18 @@ def run_reference(args: argparse.Namespace) -> None:
     print(json.dumps(line))
 
 
-def model_throughput(torch, ff, dist, world: int, timed) -> dict | None:  # noqa: ANN001
-    """images/s of the kernels-mode ViT-L/14 encoder at 518 px, batch 4 per GPU (aggregate over ranks)."""
+def model_throughput(torch, ff, world: int, timed) -> dict | None:  # noqa: ANN001
+    """images/s of the kernels-mode ViT-L/14 encoder at 518 px, batch 4 per GPU (aggregate over ranks, weak scaling),
+    device-timed with the images resident, and end to end: images from pinned host memory in, features to pinned
+    host memory out, every forward."""
     from fastforks_b200.vit import CONFIGS, ViTEncoder, seeded_state
 
     cfg = CONFIGS["dinov2-vitl14"]
     batch, side, steps = 4, 518, 5
     enc = ViTEncoder(cfg, seeded_state(cfg, 0), device="cuda", dtype=torch.bfloat16)
-    images = torch.rand(batch, 3, side, side, generator=torch.Generator().manual_seed(1)).cuda()
+    host_images = torch.rand(batch, 3, side, side, generator=torch.Generator().manual_seed(1)).pin_memory()
+    images = host_images.cuda()
+    host_out = torch.empty(batch, cfg.tokens(side, side), cfg.dim, dtype=torch.bfloat16).pin_memory()
     out = None
     for _ in range(3):
         out = enc(images)
@@ -234,7 +254,13 @@ def model_throughput(torch, ff, dist, world: int, timed) -> dict | None:  # noqa
     def forward() -> None:
         enc(images)
 
+    def forward_e2e() -> None:
+        host_out.copy_(enc(host_images.cuda(non_blocking=True)), non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the features are in host memory when the call returns
+
     ms = timed(forward, steps)
+    forward_e2e()
+    ms_e2e = timed(forward_e2e, steps)
     if ff.device_status() != 0 or not bool(torch.isfinite(out).all()):
         return None
     return {
@@ -243,7 +269,71 @@ def model_throughput(torch, ff, dist, world: int, timed) -> dict | None:  # noqa
         "images_per_s": batch * steps * world / (ms * 1e-3),
         "ms_per_forward": ms / steps,
         "attention_gflop_per_image": enc.attention_flops(1, side, side) / 1e9,
+        "e2e": {
+            "images_per_s": batch * steps * world / (ms_e2e * 1e-3),
+            "h2d_bytes_per_forward": host_images.numel() * 4,
+            "d2h_bytes_per_forward": host_out.numel() * 2,
+        },
     }
+
+
+PARTITION = {"model": "dinov2-vitg14", "images": 256, "side": 518, "chunk": 16, "check": 3}
+
+
+def partition_throughput(torch, ff, dist, world: int, rank: int, timed) -> dict | None:  # noqa: ANN001
+    """The partition the reference's multi-GPU rule gives (one process per GPU, images split between them, no
+    communication while a model runs: docs/usage.md:658-662, src/fastforks/_core/model.py:1006-1015): DINOv2 ViT-g/14
+    (`vit_giant2`, SwiGLU) at 518 px, bf16, 256 seeded images as contiguous ranges of 256 / G images per rank, run in
+    chunks of 16. Strong scaling: the job is the same at every G. The outputs are gathered to rank 0 AFTER the timed
+    region, where a few images are checked against the same images run alone."""
+    from fastforks_b200 import sharding
+    from fastforks_b200.vit import CONFIGS, ViTEncoder, seeded_state
+
+    cfg = CONFIGS[PARTITION["model"]]
+    total, side, chunk = PARTITION["images"], PARTITION["side"], PARTITION["chunk"]
+    enc = ViTEncoder(cfg, seeded_state(cfg, 0), device="cuda", dtype=torch.bfloat16)
+    mine = sharding.image_range(total, world, rank)
+
+    def image(i: int):  # noqa: ANN202 - every rank can make any image: seeded by its index
+        return torch.rand(3, side, side, generator=torch.Generator().manual_seed(10_000 + i))
+
+    images = torch.stack([image(i) for i in mine]).cuda().to(torch.bfloat16)
+    pooled = torch.empty(len(mine), 2 * cfg.dim, device="cuda", dtype=torch.float32)
+
+    def job() -> None:
+        for at in range(0, len(mine), chunk):
+            tokens = enc(images[at : at + chunk])
+            # what `features` models hand back: class token and mean patch token (src/fastforks/features/models/dinov2)
+            pooled[at : at + chunk] = torch.cat([tokens[:, 0], tokens[:, 1:].mean(1)], -1).float()
+
+    job()  # warm-up: cuBLAS plans, position table
+    ms = timed(job, 1)
+    if ff.device_status() != 0:
+        return None
+    t0 = time.perf_counter()
+    gathered = sharding.gather_to_rank0(pooled, total) if dist is not None else pooled
+    torch.cuda.synchronize()
+    gather_ms = (time.perf_counter() - t0) * 1e3
+    result = {
+        "name": f"{PARTITION['model']} at {side} px, bf16: {total} images split image-wise over {world} GPU(s), chunks of {chunk}",
+        "scaling": "strong",
+        "images": total,
+        "images_per_s": total / (ms * 1e-3),
+        "ms_job": ms,
+        "gather_to_rank0_ms_outside_timing": gather_ms,
+    }
+    if rank == 0:
+        picks = [0, total // 2, total - 1][: PARTITION["check"]]
+        cos = []
+        for i in picks:
+            alone = enc(image(i)[None].cuda().to(torch.bfloat16))
+            ref = torch.cat([alone[:, 0], alone[:, 1:].mean(1)], -1).float()[0]
+            cos.append(float(torch.nn.functional.cosine_similarity(ref, gathered[i], dim=0)))
+        result["cosine_vs_same_image_alone_min"] = min(cos)
+        result["finite"] = bool(torch.isfinite(gathered).all())
+    del enc, images
+    torch.cuda.empty_cache()
+    return result
 
 
 def time_launches(fn, reps: int, torch) -> float:  # noqa: ANN001
@@ -278,7 +368,10 @@ def run_ours(args: argparse.Namespace) -> None:  # noqa: PLR0915
     if world > 1:
         import torch.distributed as dist
 
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        from datetime import timedelta
+
+        # A finite limit on every collective and barrier: a rank that is gone ends the others with an error.
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=timedelta(seconds=180))
     ff.resolve_mode("kernels")  # raises when the CUDA library or a B200 is missing: no fallback is timed
 
     b, h, n, layers = WORKLOAD["batch"], WORKLOAD["heads"], WORKLOAD["tokens"], WORKLOAD["layers"]
@@ -324,13 +417,14 @@ def run_ours(args: argparse.Namespace) -> None:  # noqa: PLR0915
 
     for _ in range(max(3, args.warmup)):
         step()
+    # The K-step region is timed again and again until at least MIN_TIMED_SECONDS of device time are measured (every
+    # rank sees the same all-reduced times, so all ranks stop together); the clocks are sampled over exactly these
+    # regions. Reported: the median region, with the spread of all of them.
+    regions: list[float] = []
     with ClockSampler(local) as clocks:
-        total_ms = timed(step, args.steps)
-        # keep the device under the same load a little longer so that the 2 ms NVML sampler sees it
-        t_end = time.perf_counter() + 0.25
-        while time.perf_counter() < t_end:
-            step()
-        torch.cuda.synchronize()
+        while len(regions) < 3 or (sum(regions) < MIN_TIMED_SECONDS * 1e3 and len(regions) < 1000):
+            regions.append(timed(step, args.steps))
+    total_ms = statistics.median(regions)
     status = ff.device_status()
     if status != 0:
         msg = f"a kernel gave up a bounded wait (status {status}); the timing is void"
@@ -360,6 +454,7 @@ def run_ours(args: argparse.Namespace) -> None:  # noqa: PLR0915
             "unit": "TFLOP/s",
             "frac": achieved / peaks["bf16_tflops"],
             "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+            "traffic_source": "profile (one profiler capture of this kernel on this shape, not measured by this run)",
             "algorithmic_bytes": attention_bytes(b, h, n),
             "peak_source": f"{peak_kind} (cuBLAS bf16 burst)",
             "kernel": "attn_fwd_kernel<half, no bias>",
@@ -373,14 +468,28 @@ def run_ours(args: argparse.Namespace) -> None:  # noqa: PLR0915
         },
         gpu_launches=args.steps * layers,
         clocks=clocks.summary(),
+        timed_regions={
+            "count": len(regions),
+            "seconds": sum(regions) * 1e-3,
+            "ms_min": min(regions),
+            "ms_median": total_ms,
+            "ms_max": max(regions),
+            "spread": (max(regions) - min(regions)) / total_ms,
+        },
     )
 
     # Whole-model throughput of the caller of the hot path: the ViT-L/14 encoder of Depth-Anything-V2-L / DINOv2-L at
     # 518 px (N = 1370, 24 layers, 16 heads), bf16, random-init weights, on every rank's own images. GEMMs, LayerNorm
     # and GELU are torch library calls; the attention is this repository's kernel.
-    model = model_throughput(torch, ff, dist, world, timed)
+    model = model_throughput(torch, ff, world, timed)
     if model is not None:
         line["model"] = model
+    torch.cuda.empty_cache()
+    # The partition the benchmark list names: ViT-g/14, 256 images split image-wise over the ranks (strong scaling).
+    if not args.skip_partition:
+        partition = partition_throughput(torch, ff, dist, world, rank, timed)
+        if partition is not None:
+            line["partition"] = partition
 
     if rank == 0:
         regimes = {}
@@ -453,6 +562,7 @@ def main() -> None:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--case", choices=tuple(CASES), default=None, help="launch one kernel case for a profiler and exit")
     ap.add_argument("--launches", type=int, default=4)
+    ap.add_argument("--skip-partition", action="store_true", help="leave out the ViT-g/14 256-image partition leg")
     args = ap.parse_args()
     args.steps = max(1, args.steps)
     if args.case is not None:

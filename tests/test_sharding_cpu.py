@@ -70,3 +70,40 @@ def test_two_ranks_shard_and_gather(tmp_path: Path, total: int) -> None:
     qkv = torch.randn(total, 3, 2, 33, 64, generator=gen)
     ref = ao.attention(qkv[:, 0].numpy(), qkv[:, 1].numpy(), qkv[:, 2].numpy())
     np.testing.assert_allclose(np.load(out_path), ref, rtol=0, atol=1e-6)
+
+
+def _leaver_worker(rank: int, world: int, port: int, out_dir: str) -> None:
+    """Two steps of independent shard work, a barrier after each. Rank 1 leaves between the steps (it returns without
+    joining the second barrier and without destroying the group, as a process that is gone would); rank 0's second
+    barrier must end with an error within the group's timeout instead of waiting for ever."""
+    import time
+    from datetime import timedelta
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=5))
+    dist.barrier()  # step 1: everybody is here
+    if rank == 1:
+        os._exit(0)  # noqa: SLF001 - leaves between steps, nothing of it in flight
+    t0 = time.monotonic()
+    outcome = "completed"
+    try:
+        dist.barrier()  # step 2: rank 1 never comes
+    except Exception as e:  # noqa: BLE001 - gloo reports the lost peer or the timeout as RuntimeError / DistBackendError
+        outcome = f"error after {time.monotonic() - t0:.1f} s: {type(e).__name__}"
+    Path(out_dir, f"rank{rank}.txt").write_text(outcome)
+    os._exit(0)  # noqa: SLF001 - the group is broken: no orderly shutdown to wait for
+
+
+def test_a_rank_that_leaves_between_steps_ends_the_others_barrier_with_an_error(tmp_path: Path) -> None:
+    """The host-side failure form of the multi-GPU harness: no collective runs while a model runs, so a lost rank
+    shows at the next barrier, which has a finite limit (bench.py gives its process group one too)."""
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_leaver_worker, args=(r, 2, port, str(tmp_path))) for port in [_free_port()] for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        assert not p.is_alive(), "a rank is still waiting: the barrier has no limit"
+    outcome = (tmp_path / "rank0.txt").read_text()
+    assert outcome.startswith("error after"), outcome
+    assert float(outcome.split()[2]) < 30.0
