@@ -187,6 +187,20 @@ class ViTEncoder:
         c = x.shape[-1]
         return F.layer_norm(x, (c,), self.w["norm.weight"], self.w["norm.bias"], self.cfg.eps)
 
+    @torch.no_grad()
+    def intermediate(self, images: torch.Tensor, layers: tuple[int, ...]) -> list[torch.Tensor]:
+        """Normalised tokens after the blocks in `layers`: what the depth models hand to their DPT head
+        (upstream `get_intermediate_layers(..., norm=True)`, net/dinov2.py:300-336; Depth-Anything-V2-L takes blocks
+        4, 11, 17, 23)."""
+        x = self.tokens(images.to(self.device))
+        c = x.shape[-1]
+        outs = []
+        for i in range(max(layers) + 1):
+            x = self.block(i, x)
+            if i in layers:
+                outs.append(F.layer_norm(x, (c,), self.w["norm.weight"], self.w["norm.bias"], self.cfg.eps))
+        return outs
+
     def attention_flops(self, batch: int, height: int, width: int) -> float:
         """FLOPs of the attention calls of one forward: depth * 4 * B * heads * N^2 * 64."""
         n = self.cfg.tokens(height, width)

@@ -2,7 +2,7 @@
 
 Run where the reference checkout is available (it is not on the GPU machines, so the outputs are committed):
 
-    python tests/golden/make_golden.py /path/to/fastforks
+    python tests/golden/make_golden.py /path/to/fastforks [case ...]
 
 For each case a reference attention module (seeded random weights, fp32, CPU) is run on a seeded input; hooks on
 its `qkv` and `proj` layers capture the hot path's inputs (q, k, v after the projection) and its output (the tensor
@@ -124,6 +124,113 @@ def dinov2_model_case(seed: int, name: str, hw: tuple[int, int], qk_gain: float)
             "qk_gain": np.float32(qk_gain)}  # fmt: skip
 
 
+def _sample_tokens(tokens: torch.Tensor, every: int) -> torch.Tensor:
+    """Class token and every `every`-th patch token: enough for a cosine check, small enough to commit."""
+    return torch.cat([tokens[:, :1], tokens[:, 1::every]], 1)
+
+
+def dinov2_block_case(seed: int, name: str, depth: int, hw: tuple[int, int], qk_gain: float) -> dict[str, np.ndarray]:
+    """The first `depth` blocks of a vendored DINOv2 network (for ViT-g/14: the fused SwiGLU feed-forward) on seeded
+    weights: the reference constructor is called with that depth, everything else as `DINOv2(name)` does."""
+    import dataclasses
+
+    sys.path.insert(0, str(HERE.parent.parent))
+    from fastforks.shared.depth_anything_v2.net import dinov2 as ref
+
+    from fastforks_b200.vit import CONFIGS, seeded_state
+
+    cfg = dataclasses.replace(CONFIGS[name], depth=depth)
+    from functools import partial
+
+    # `vit_giant2` / `vit_large` (net/dinov2.py:385-420) fix the depth: the same constructor call with `depth` blocks
+    net = ref.DinoVisionTransformer(
+        patch_size=14, embed_dim=cfg.dim, depth=depth, num_heads=cfg.heads, mlp_ratio=4,
+        block_fn=partial(ref.Block, attn_class=ref.MemEffAttention), num_register_tokens=0, img_size=518, init_values=1.0,
+        ffn_layer="swiglufused" if cfg.ffn == "swiglu" else "mlp", block_chunks=0, interpolate_antialias=False,
+        interpolate_offset=0.1,
+    ).eval()  # fmt: skip
+    state = seeded_state(cfg, seed, qk_gain=qk_gain)
+    assert list(net.state_dict()) == list(state), "parameter names / order differ from the reference network"
+    net.load_state_dict(state, strict=True)
+    images = torch.rand(1, 3, *hw, generator=torch.Generator().manual_seed(seed + 1))
+    with torch.no_grad():
+        feats = net.forward_features(images)
+    tokens = torch.cat([feats["x_norm_clstoken"][:, None], feats["x_norm_patchtokens"]], 1)
+    return {"out": tokens.half(), "seed": np.int64(seed), "image_seed": np.int64(seed + 1), "hw": np.array(hw, dtype=np.int32),
+            "qk_gain": np.float32(qk_gain), "depth": np.int64(depth)}  # fmt: skip
+
+
+def dinov2_518_case(seed: int, name: str, qk_gain: float, every: int) -> dict[str, np.ndarray]:
+    """ViT-S/14 at 518 x 518: N = 1370 tokens, the long-sequence kernel inside a whole model."""
+    case = dinov2_model_case(seed, name, (518, 518), qk_gain)
+    case["out"] = _sample_tokens(case["out"], every).half()
+    case["every"] = np.int64(every)
+    return case
+
+
+def dav2_encoder_case(seed: int, qk_gain: float, every: int) -> dict[str, np.ndarray]:
+    """Depth-Anything-V2-L's encoder as its depth model calls it: `get_intermediate_layers` of ViT-L/14 at 518 px for
+    blocks 4, 11, 17, 23 with class tokens (src/fastforks/shared/depth_anything_v2/net/dpt.py:176-191). The DPT head
+    behind it is convolutions only and is not part of the fixture."""
+    sys.path.insert(0, str(HERE.parent.parent))
+    from fastforks.shared.depth_anything_v2 import DINOv2
+
+    from fastforks_b200.vit import CONFIGS, seeded_state
+
+    cfg = CONFIGS["dinov2-vitl14"]
+    net = DINOv2("vitl").eval()
+    state = seeded_state(cfg, seed, qk_gain=qk_gain)
+    net.load_state_dict(state, strict=True)
+    images = torch.rand(1, 3, 518, 518, generator=torch.Generator().manual_seed(seed + 1))
+    layers = [4, 11, 17, 23]
+    with torch.no_grad():
+        feats = net.get_intermediate_layers(images, layers, return_class_token=True)
+    out = torch.stack([torch.cat([cls[:, None], patches[:, ::every]], 1) for patches, cls in feats])  # [4, 1, 1 + n, C]
+    return {"out": out.half(), "seed": np.int64(seed), "image_seed": np.int64(seed + 1), "qk_gain": np.float32(qk_gain),
+            "layers": np.array(layers, dtype=np.int32), "every": np.int64(every)}  # fmt: skip
+
+
+def timm_blocks_case(seed: int, qk_gain: float) -> dict[str, np.ndarray]:
+    """The twelve blocks of `vit_base_patch16_224` (src/fastforks/shared/timm_blocks/net/vit.py:51-85) on seeded tokens
+    `[1, 197, 768]`: the reference builds only the blocks (patch embedding and head come from the caller's model)."""
+    sys.path.insert(0, str(HERE.parent.parent))
+    from fastforks.shared.timm_blocks.net.vit import create_vit_blocks
+
+    from fastforks_b200.vit import CONFIGS, seeded_state
+
+    cfg = CONFIGS["vit-b16"]
+    net = create_vit_blocks("vit_base_patch16_224").eval()
+    state = seeded_state(cfg, seed, qk_gain=qk_gain)
+    blocks = {k: v for k, v in state.items() if k.startswith("blocks.")}
+    assert list(net.state_dict()) == list(blocks), "parameter names / order differ from the reference blocks"
+    net.load_state_dict(blocks, strict=True)
+    tokens = torch.randn(1, 197, cfg.dim, generator=torch.Generator().manual_seed(seed + 1))
+    with torch.no_grad():
+        out = net.blocks(tokens)
+    return {"out": out.half(), "seed": np.int64(seed), "token_seed": np.int64(seed + 1), "qk_gain": np.float32(qk_gain)}
+
+
+def sam_encoder_case(seed: int, every: int) -> dict[str, np.ndarray]:
+    """SAM ViT-B's image encoder at 1024 x 1024 (8 windowed and 4 global blocks, relative-position tables filled:
+    upstream initialises them to zero) on seeded weights; stored: every `every`-th position of the 64 x 64 output."""
+    sys.path.insert(0, str(HERE.parent.parent))
+    from fastforks.promptable_segmentation.models.sam.net.image_encoder import ImageEncoderViT
+
+    from fastforks_b200.sam import SAM_VIT_B, sam_seeded_state
+
+    cfg = SAM_VIT_B
+    net = ImageEncoderViT(img_size=cfg.img, patch_size=cfg.patch, embed_dim=cfg.dim, depth=cfg.depth, num_heads=cfg.heads,
+                          out_chans=cfg.out_chans, use_rel_pos=True, window_size=cfg.window,
+                          global_attn_indexes=cfg.global_blocks, norm_layer=torch.nn.LayerNorm).eval()  # fmt: skip
+    state = sam_seeded_state(cfg, seed)
+    assert list(net.state_dict()) == list(state), "parameter names / order differ from the reference encoder"
+    net.load_state_dict(state, strict=True)
+    images = torch.rand(1, 3, cfg.img, cfg.img, generator=torch.Generator().manual_seed(seed + 1))
+    with torch.no_grad():
+        out = net(images)
+    return {"out": out[:, :, ::every, ::every].half(), "seed": np.int64(seed), "image_seed": np.int64(seed + 1), "every": np.int64(every)}
+
+
 CASES = {
     # name: (builder, kwargs). Token counts follow the reference: 97 = its feature-golden input (112x168, patch 14),
     # 197 = ViT-B/16 at 224, 196 = one 14x14 SAM window; 8x16 exercises kh != kw.
@@ -135,17 +242,28 @@ CASES = {
     # whole encoder, N = 1 + 16 * 12 = 193 tokens (a non-square grid exercises the position interpolation)
     "model_dinov2_vits14": (dinov2_model_case, {"seed": 7, "name": "dinov2-vits14", "hw": (224, 168), "qk_gain": 1.0}),
     "model_dinov2_vits14_sharp": (dinov2_model_case, {"seed": 8, "name": "dinov2-vits14", "hw": (224, 224), "qk_gain": 8.0}),
+    # N = 1370 inside a whole model; one SwiGLU block of ViT-g/14; the encoder call of Depth-Anything-V2-L; the blocks of
+    # timm's ViT-B/16; SAM ViT-B's encoder. Outputs are stored as fp16 samples: the checks are cosine checks.
+    "model_dinov2_vits14_518": (dinov2_518_case, {"seed": 9, "name": "dinov2-vits14", "qk_gain": 4.0, "every": 4}),
+    "model_dinov2_vitg14_block": (dinov2_block_case, {"seed": 10, "name": "dinov2-vitg14", "depth": 1, "hw": (224, 168), "qk_gain": 4.0}),
+    "model_dav2l_encoder_518": (dav2_encoder_case, {"seed": 11, "qk_gain": 4.0, "every": 8}),
+    "model_timm_vitb16_blocks": (timm_blocks_case, {"seed": 12, "qk_gain": 4.0}),
+    "model_sam_vitb_1024": (sam_encoder_case, {"seed": 13, "every": 2}),
 }
 
 
 def main() -> None:
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
-    _import_reference(root)
-    torch.set_num_threads(1)  # one thread: bit-stable sums
-    for name, (fn, kwargs) in CASES.items():
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/fastforks [case ...]")
+    _import_reference(Path(sys.argv[1]))
+    wanted = sys.argv[2:] or list(CASES)
+    for name in wanted:
+        fn, kwargs = CASES[name]
+        torch.set_num_threads(1 if not name.startswith("model_") else 8)  # op-level cases: one thread, bit-stable sums
         case = fn(**kwargs)
         arrays = {k: (v.contiguous().numpy() if isinstance(v, torch.Tensor) else np.asarray(v)) for k, v in case.items()}
-        np.savez(HERE / f"{name}.npz", **arrays)
+        (np.savez_compressed if name.startswith("model_") and name not in ("model_dinov2_vits14", "model_dinov2_vits14_sharp")
+         else np.savez)(HERE / f"{name}.npz", **arrays)  # fmt: skip
         print(name, {k: a.shape for k, a in arrays.items()})
 
 
