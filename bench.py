@@ -261,6 +261,11 @@ def model_throughput(torch, ff, world: int, timed) -> dict | None:  # noqa: ANN0
     ms = timed(forward, steps)
     forward_e2e()
     ms_e2e = timed(forward_e2e, steps)
+    own = ViTEncoder(cfg, seeded_state(cfg, 0), device="cuda", dtype=torch.bfloat16, fuse_plain=True)
+    for _ in range(2):
+        own(images)
+    ms_own = timed(lambda: own(images), steps)
+    del own
     if ff.device_status() != 0 or not bool(torch.isfinite(out).all()):
         return None
     return {
@@ -269,6 +274,8 @@ def model_throughput(torch, ff, world: int, timed) -> dict | None:  # noqa: ANN0
         "images_per_s": batch * steps * world / (ms * 1e-3),
         "ms_per_forward": ms / steps,
         "attention_gflop_per_image": enc.attention_flops(1, side, side) / 1e9,
+        "linear_layers": "proj, fc1, fc2 on this library's GEMM with fused epilogue; qkv (bias only) on torch's library GEMM",
+        "images_per_s_every_linear_layer_own_gemm": batch * steps * world / (ms_own * 1e-3),
         "e2e": {
             "images_per_s": batch * steps * world / (ms_e2e * 1e-3),
             "h2d_bytes_per_forward": host_images.numel() * 4,

@@ -15,11 +15,17 @@ from . import _lib
 from ._lib import build
 from .attention import attention, check_operands, device_status, reserve_workspace
 from .errors import BackendUnavailableError, KernelUnavailableError
+from .gemm import ACT_GELU, ACT_GELU_TANH, ACT_NONE, ACT_RELU, gemm
 from .flash64 import FLASH_VARIANTS, Flash64, check_flash64
 from .host_io import HostAttention
+from .sam import sam_rel_terms
 from .sdpa import scaled_dot_product_attention
 
 __all__ = [
+    "ACT_GELU",
+    "ACT_GELU_TANH",
+    "ACT_NONE",
+    "ACT_RELU",
     "FLASH_VARIANTS",
     "BackendUnavailableError",
     "Flash64",
@@ -30,9 +36,11 @@ __all__ = [
     "check_flash64",
     "check_operands",
     "device_status",
+    "gemm",
     "kernels_unavailable_reason",
     "reserve_workspace",
     "resolve_mode",
+    "sam_rel_terms",
     "scaled_dot_product_attention",
     "version",
 ]

@@ -25,6 +25,8 @@ SOURCE = PACKAGE_DIR / "csrc" / "b200_attn.cu"
 HEADERS = (
     PACKAGE_DIR / "csrc" / "sm100_ptx.cuh",
     PACKAGE_DIR / "csrc" / "attn_fwd_sm100.cuh",
+    PACKAGE_DIR / "csrc" / "sam_rel_terms.cuh",
+    PACKAGE_DIR / "csrc" / "gemm_sm100.cuh",
     PACKAGE_DIR.parent / "include" / "b200_attn.h",
 )
 SHARED_OBJECT = PACKAGE_DIR / "libb200attn.so"
@@ -37,7 +39,7 @@ NVCC_FLAGS = (
 
 # Every symbol include/b200_attn.h declares.
 EXPORTS = (
-    "b200_attn_fwd", "b200_attn_fwd_static", "b200_attn_query", "b200_attn_plan", "b200_attn_workspace_size", "b200_attn_status",
+    "b200_attn_fwd", "b200_attn_fwd_static", "b200_gemm", "b200_sam_rel_terms", "b200_attn_query", "b200_attn_plan", "b200_attn_workspace_size", "b200_attn_status",
     "b200_attn_selftest_wait_limit", "b200_attn_last_error", "b200_attn_version",
 )  # fmt: skip
 
@@ -80,6 +82,47 @@ class B200AttnArgs(ctypes.Structure):
         ("test_flags", ctypes.c_int32),
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_int64),
+    )
+
+
+class B200GemmArgs(ctypes.Structure):
+    """Mirror of `struct B200GemmArgs` (include/b200_attn.h)."""
+
+    _fields_ = (
+        ("struct_size", ctypes.c_uint32),
+        ("dtype", ctypes.c_uint32),
+        ("m", ctypes.c_int32),
+        ("n", ctypes.c_int32),
+        ("k", ctypes.c_int32),
+        ("act", ctypes.c_int32),
+        ("x", ctypes.c_void_p),
+        ("lda", ctypes.c_int64),
+        ("w", ctypes.c_void_p),
+        ("bias", ctypes.c_void_p),
+        ("scale", ctypes.c_void_p),
+        ("res", ctypes.c_void_p),
+        ("lres", ctypes.c_int64),
+        ("y", ctypes.c_void_p),
+        ("ldy", ctypes.c_int64),
+    )
+
+
+class B200RelTermsArgs(ctypes.Structure):
+    """Mirror of `struct B200RelTermsArgs` (include/b200_attn.h)."""
+
+    _fields_ = (
+        ("struct_size", ctypes.c_uint32),
+        ("dtype", ctypes.c_uint32),
+        ("q", ctypes.c_void_p),
+        ("q_stride", ctypes.c_int64 * 3),
+        ("rel_pos_h", ctypes.c_void_p),
+        ("rel_pos_w", ctypes.c_void_p),
+        ("rel_h", ctypes.c_void_p),
+        ("rel_w", ctypes.c_void_p),
+        ("batch", ctypes.c_int32),
+        ("heads", ctypes.c_int32),
+        ("side", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32),
     )
 
 
@@ -159,6 +202,10 @@ def library() -> ctypes.CDLL:
     lib.b200_attn_fwd.restype = ctypes.c_int
     lib.b200_attn_fwd_static.argtypes = (ctypes.POINTER(B200AttnArgs), ctypes.c_void_p)
     lib.b200_attn_fwd_static.restype = ctypes.c_int
+    lib.b200_gemm.argtypes = (ctypes.POINTER(B200GemmArgs), ctypes.c_void_p)
+    lib.b200_gemm.restype = ctypes.c_int
+    lib.b200_sam_rel_terms.argtypes = (ctypes.POINTER(B200RelTermsArgs), ctypes.c_void_p)
+    lib.b200_sam_rel_terms.restype = ctypes.c_int
     lib.b200_attn_query.argtypes = (ctypes.POINTER(B200AttnArgs), ctypes.POINTER(ctypes.c_int32))
     lib.b200_attn_query.restype = ctypes.c_int
     i32p = ctypes.POINTER(ctypes.c_int32)

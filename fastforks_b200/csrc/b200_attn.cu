@@ -16,6 +16,8 @@
 #include <type_traits>
 
 #include "attn_fwd_sm100.cuh"
+#include "gemm_sm100.cuh"
+#include "sam_rel_terms.cuh"
 
 namespace {
 
@@ -200,6 +202,7 @@ struct DeviceState {
   int sms = 0;
   uint32_t* status = nullptr;
   std::atomic<bool> opted_in[kKernelForms];
+  std::atomic<bool> gemm_opted_in[6];  // 2 dtypes x 3 tile shapes
 };
 DeviceState g_devices[kMaxDevices];
 std::mutex g_devices_mutex;
@@ -219,6 +222,7 @@ int device_state(DeviceState** out) {
       e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status), g_status_word);
       if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(status word)");
       for (auto& f : d.opted_in) f.store(false, std::memory_order_relaxed);
+      for (auto& f : d.gemm_opted_in) f.store(false, std::memory_order_relaxed);
       d.ready.store(true, std::memory_order_release);
     }
   }
@@ -562,6 +566,156 @@ int b200_attn_fwd_static(const B200AttnArgs* a, void* stream_ptr) {
                       static_cast<size_t>(dev->sms) * 2 * sizeof(uint32_t), static_cast<cudaStream_t>(stream_ptr));
   if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(counters of the built-in scratch array)");
   return b200_attn_fwd(&with_scratch, stream_ptr);
+}
+
+// Per SM and clock: what the tensor pipe delivers in a GEMM under the power cap (measured with cuBLAS: 1.4 PFLOP/s
+// over 148 SMs at 1.9 GHz) and what the L2 delivers to one SM when all of them pull (about 10 TB/s).
+constexpr double kGemmPipeFlopsPerClock = 5000.0, kGemmL2BytesPerClock = 36.0;
+
+int b200_gemm(const B200GemmArgs* a, void* stream_ptr) {
+  if (a == nullptr) return fail(B200_ATTN_BAD_CONFIG, "args is NULL");
+  if (a->struct_size != sizeof(B200GemmArgs))
+    return fail(B200_ATTN_BAD_CONFIG, "struct_size %u does not match this library's B200GemmArgs (%zu bytes)", a->struct_size,
+                sizeof(B200GemmArgs));
+  if (a->dtype != B200_ATTN_F16 && a->dtype != B200_ATTN_BF16)
+    return fail(B200_ATTN_BAD_CONFIG, "dtype %u: x, w, bias, res, y must be fp16 (0) or bf16 (1)", a->dtype);
+  if (a->act != kActNone && a->act != kActRelu && a->act != kActGelu && a->act != kActGeluTanh)
+    return fail(B200_ATTN_BAD_CONFIG, "act %d: 0 none, 1 relu, 5 gelu (erf), 6 gelu (tanh form)", a->act);
+  if (a->m < 1 || a->n < 1 || a->k < 1 || a->n % 8 != 0 || a->k % 8 != 0)
+    return fail(B200_ATTN_UNSUPPORTED, "m %d n %d k %d: all positive, n and k multiples of 8", a->m, a->n, a->k);
+  if (a->lda < a->k || a->lda % 8 != 0 || a->ldy < a->n || a->ldy % 8 != 0 || (a->res != nullptr && (a->lres < a->n || a->lres % 8 != 0)))
+    return fail(B200_ATTN_UNSUPPORTED, "row strides lda %lld ldy %lld lres %lld must cover their rows and be multiples of 8",
+                static_cast<long long>(a->lda), static_cast<long long>(a->ldy), static_cast<long long>(a->lres));
+  if (a->lda >= (int64_t(1) << 38)) return fail(B200_ATTN_UNSUPPORTED, "lda too large for a tensor map");
+  const struct { const char* name; const void* ptr; bool required; } ptrs[] = {
+      {"x", a->x, true}, {"w", a->w, true}, {"y", a->y, true}, {"bias", a->bias, false}, {"scale", a->scale, false}, {"res", a->res, false}};
+  for (const auto& x : ptrs) {
+    if (x.ptr == nullptr && x.required) return fail(B200_ATTN_BAD_CONFIG, "%s is NULL", x.name);
+    if (!aligned16(x.ptr)) return fail(B200_ATTN_UNSUPPORTED, "%s is not 16-byte aligned", x.name);
+  }
+  DeviceState* dev = nullptr;
+  if (int rc = device_state(&dev)) return rc;
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr) return fail(B200_ATTN_CUDA_ERROR_BASE, "cuTensorMapEncodeTiled is not available from this driver");
+  const CUtensorMapDataType dt = a->dtype == B200_ATTN_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap mx, mw;
+  const cuuint32_t box[2] = {kGemmBK, 128}, elem[2] = {1, 1};
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a->k), static_cast<cuuint64_t>(a->m)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a->lda) * 2};
+    const CUresult r = enc(&mx, dt, 2, const_cast<void*>(a->x), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200_ATTN_UNSUPPORTED, "tensor map for x rejected by the driver (CUresult %d)", static_cast<int>(r));
+  }
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a->k), static_cast<cuuint64_t>(a->n)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a->k) * 2};
+    const CUresult r = enc(&mw, dt, 2, const_cast<void*>(a->w), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200_ATTN_UNSUPPORTED, "tensor map for w rejected by the driver (CUresult %d)", static_cast<int>(r));
+  }
+  GemmParams prm{};
+  prm.m = a->m; prm.n = a->n; prm.k = a->k;
+  prm.bias = a->bias; prm.scale = a->scale; prm.res = a->res; prm.lres = a->lres;
+  prm.y = a->y; prm.ldy = a->ldy; prm.act = a->act;
+  prm.status = dev->status;
+  // Tile shape: of 128 x 128, 128 x 256 and 256 x 256 the one with the shortest estimated time. A tile's time is its
+  // flops over the rate its shape allows - the tensor pipe, or the L2 bandwidth times the flops the tile gets out of
+  // a byte (2 BM BN / (2 (BM + BN)) per k-value) - and the tiles run in rounds of one per SM.
+  struct Shape { int bm, bn; } shapes[3] = {{128, 128}, {128, 256}, {256, 256}};
+  int best = 0;
+  double best_time = 0;
+  for (int i = 0; i < 3; ++i) {
+    if (shapes[i].bn > 128 && a->n <= 128) continue;
+    if (shapes[i].bm > 128 && a->m <= 128) continue;
+    const long long tm = (a->m + shapes[i].bm - 1) / shapes[i].bm, tn = (a->n + shapes[i].bn - 1) / shapes[i].bn;
+    const double rounds = static_cast<double>((tm * tn + dev->sms - 1) / dev->sms);
+    const double flops_per_byte = static_cast<double>(shapes[i].bm) * shapes[i].bn / (shapes[i].bm + shapes[i].bn);
+    const double rate = std::min(kGemmPipeFlopsPerClock, kGemmL2BytesPerClock * flops_per_byte);
+    const double time = rounds * (2.0 * shapes[i].bm * shapes[i].bn) / rate;
+    if (i == 0 || time < best_time) {
+      best = i;
+      best_time = time;
+    }
+  }
+  const int bm = shapes[best].bm, bn = shapes[best].bn;
+  prm.tiles_m = (a->m + bm - 1) / bm;
+  prm.tiles_n = (a->n + bn - 1) / bn;
+  const long long tiles = static_cast<long long>(prm.tiles_m) * prm.tiles_n;
+  if (tiles > 0x7fffffffLL) return fail(B200_ATTN_UNSUPPORTED, "problem too large for one launch");
+  const unsigned grid = static_cast<unsigned>(std::min<long long>(tiles, dev->sms));
+  const bool f16 = a->dtype == B200_ATTN_F16;
+  const int form = (f16 ? 0 : 1) * 3 + best;
+  const void* kernels[6] = {
+      reinterpret_cast<const void*>(gemm_epilogue_kernel<__half, 128, 128>), reinterpret_cast<const void*>(gemm_epilogue_kernel<__half, 128, 256>),
+      reinterpret_cast<const void*>(gemm_epilogue_kernel<__half, 256, 256>), reinterpret_cast<const void*>(gemm_epilogue_kernel<__nv_bfloat16, 128, 128>),
+      reinterpret_cast<const void*>(gemm_epilogue_kernel<__nv_bfloat16, 128, 256>), reinterpret_cast<const void*>(gemm_epilogue_kernel<__nv_bfloat16, 256, 256>)};
+  const void* kernel = kernels[form];
+  const size_t smem_of[3] = {sizeof(GemmSmem<128, 128>), sizeof(GemmSmem<128, 256>), sizeof(GemmSmem<256, 256>)};
+  const int smem = static_cast<int>(smem_of[best]) + 1024;
+  if (!dev->gemm_opted_in[form].load(std::memory_order_acquire)) {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(shared memory)");
+    dev->gemm_opted_in[form].store(true, std::memory_order_release);
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(kGemmThreads);
+  config.dynamicSmemBytes = smem;
+  config.stream = static_cast<cudaStream_t>(stream_ptr);
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  void* kargs[] = {&mx, &mw, &prm};
+  cudaError_t e = cudaLaunchKernelExC(&config, kernel, kargs);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "gemm kernel launch");
+  tl_error[0] = '\0';
+  return B200_ATTN_OK;
+}
+
+int b200_sam_rel_terms(const B200RelTermsArgs* a, void* stream_ptr) {
+  if (a == nullptr) return fail(B200_ATTN_BAD_CONFIG, "args is NULL");
+  if (a->struct_size != sizeof(B200RelTermsArgs))
+    return fail(B200_ATTN_BAD_CONFIG, "struct_size %u does not match this library's B200RelTermsArgs (%zu bytes)",
+                a->struct_size, sizeof(B200RelTermsArgs));
+  if (a->dtype != B200_ATTN_F16 && a->dtype != B200_ATTN_BF16)
+    return fail(B200_ATTN_BAD_CONFIG, "dtype %u: q, the tables and the results must be fp16 (0) or bf16 (1)", a->dtype);
+  if (a->head_dim != kHeadDim) return fail(B200_ATTN_UNSUPPORTED, "head_dim %d: only head dim 64 is built", a->head_dim);
+  if (a->batch < 1 || a->heads < 1 || a->side < 2 || a->side > kRelMaxSide || a->side % 2 != 0)
+    return fail(B200_ATTN_UNSUPPORTED, "batch %d heads %d side %d: side must be even, 2 .. %d", a->batch, a->heads, a->side, kRelMaxSide);
+  if (static_cast<int64_t>(a->batch) * a->side > 0x7fffffffLL) return fail(B200_ATTN_UNSUPPORTED, "batch too large for one launch");
+  const int tokens = a->side * a->side;
+  if (int rc = check_view("q", a->q, a->q_stride, a->batch, a->heads, tokens)) return rc;
+  const struct { const char* name; const void* ptr; int align; } ptrs[] = {
+      {"rel_pos_h", a->rel_pos_h, 4}, {"rel_pos_w", a->rel_pos_w, 4}, {"rel_h", a->rel_h, 4}, {"rel_w", a->rel_w, 4}};
+  for (const auto& x : ptrs) {
+    if (x.ptr == nullptr) return fail(B200_ATTN_BAD_CONFIG, "%s is NULL", x.name);
+    if (reinterpret_cast<uintptr_t>(x.ptr) % x.align != 0) return fail(B200_ATTN_UNSUPPORTED, "%s is not 4-byte aligned", x.name);
+  }
+  RelTermsParams prm{};
+  prm.q = a->q;
+  prm.q_sb = a->q_stride[0];
+  prm.q_sn = a->q_stride[1];
+  prm.q_sh = a->q_stride[2];
+  prm.rel_pos_h = a->rel_pos_h;
+  prm.rel_pos_w = a->rel_pos_w;
+  prm.rel_h = a->rel_h;
+  prm.rel_w = a->rel_w;
+  prm.batch = a->batch;
+  prm.heads = a->heads;
+  prm.side = a->side;
+  const int rows = a->side * a->heads;
+  const dim3 grid(static_cast<unsigned>(a->batch * a->side), 2, static_cast<unsigned>(std::min(8, (rows + kRelThreads - 1) / kRelThreads)));
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  if (a->dtype == B200_ATTN_F16) sam_rel_terms_kernel<__half><<<grid, kRelThreads, 0, stream>>>(prm);
+  else sam_rel_terms_kernel<__nv_bfloat16><<<grid, kRelThreads, 0, stream>>>(prm);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "sam_rel_terms kernel launch");
+  tl_error[0] = '\0';
+  return B200_ATTN_OK;
 }
 
 int b200_attn_status(uint32_t* status) {

@@ -97,6 +97,56 @@ def rel_table(size: int, rel_pos: torch.Tensor) -> torch.Tensor:
     return rel_pos[(idx[:, None] - idx[None, :]) + (size - 1)]
 
 
+def sam_rel_terms(q: torch.Tensor, rel_pos_h: torch.Tensor, rel_pos_w: torch.Tensor, side: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """`rel_h`, `rel_w` `[B, heads, N, side]` for `attention(..., rel=)`, on the B200 kernel (`b200_sam_rel_terms`).
+
+    Args:
+        q: UNSCALED queries, fp16 / bf16 CUDA `[B, N, heads, 64]` with N = side * side (row-major grid), a strided view
+            of the packed qkv tensor is fine (unit last stride, other strides multiples of 8).
+        rel_pos_h: The attention module's parameter `[2 * side - 1, 64]`, same dtype and device (made contiguous if not).
+        rel_pos_w: Likewise.
+        side: Even, at most 64 (14 for SAM's windows, 64 for its global blocks).
+
+    Replaces `get_rel_pos` and the two einsums of the reference's `augmented`
+    (`src/fastforks/promptable_segmentation/models/sam/fast.py:104-106`): q is read once, nothing else is materialised.
+
+    Raises:
+        ValueError: Operands outside the contract (checked before the launch).
+    """
+    import ctypes
+
+    from . import _lib
+
+    if q.dim() != 4 or q.shape[-1] != 64 or q.stride(-1) != 1 or not q.is_cuda or q.dtype not in (torch.float16, torch.bfloat16):  # noqa: PLR2004
+        msg = f"sam_rel_terms: q must be a float16 / bfloat16 CUDA [B, N, heads, 64] view with unit last stride, got {tuple(q.shape)} {q.dtype} {q.device}"
+        raise ValueError(msg)
+    b, n, heads, _ = q.shape
+    if side % 2 != 0 or not 2 <= side <= 64:  # noqa: PLR2004
+        msg = f"sam_rel_terms: side {side} must be even, 2 .. 64"
+        raise ValueError(msg)
+    if n != side * side:
+        msg = f"sam_rel_terms: {n} tokens is not a {side} x {side} grid"
+        raise ValueError(msg)
+    for name, t in (("rel_pos_h", rel_pos_h), ("rel_pos_w", rel_pos_w)):
+        if t.shape != (2 * side - 1, 64) or t.dtype != q.dtype or t.device != q.device:
+            msg = f"sam_rel_terms: {name} must be [{2 * side - 1}, 64] {q.dtype} on {q.device}, got {tuple(t.shape)} {t.dtype} {t.device}"
+            raise ValueError(msg)
+    rel_pos_h, rel_pos_w = rel_pos_h.contiguous(), rel_pos_w.contiguous()
+    rel_h = torch.empty(b, heads, n, side, device=q.device, dtype=q.dtype)
+    rel_w = torch.empty_like(rel_h)
+    a = _lib.B200RelTermsArgs()
+    a.struct_size = ctypes.sizeof(_lib.B200RelTermsArgs)
+    a.dtype = _lib.F16 if q.dtype == torch.float16 else _lib.BF16
+    a.q = q.data_ptr()
+    a.q_stride[:] = (q.stride(0), q.stride(1), q.stride(2))
+    a.rel_pos_h, a.rel_pos_w, a.rel_h, a.rel_w = rel_pos_h.data_ptr(), rel_pos_w.data_ptr(), rel_h.data_ptr(), rel_w.data_ptr()
+    a.batch, a.heads, a.side, a.head_dim = b, heads, side, 64
+    with torch.cuda.device(q.device):
+        code = _lib.library().b200_sam_rel_terms(ctypes.byref(a), torch._C._cuda_getCurrentRawStream(q.device.index))  # noqa: SLF001
+    _lib.raise_for_code(code, "sam_rel_terms")
+    return rel_h, rel_w
+
+
 def rel_terms(q: torch.Tensor, table_h: torch.Tensor, table_w: torch.Tensor, side: int) -> tuple[torch.Tensor, torch.Tensor]:
     """`rel_h`, `rel_w` `[B, heads, N, side]` from the UNSCALED q `[B, N, heads, d]` (N = side * side, row-major) and
     the tables of `rel_table`: `rel_h[b, n, (y, x), k] = q[b, (y, x), n] . table_h[y, k]`, `rel_w` with `table_w[x, k]`
@@ -133,7 +183,11 @@ class SamEncoder:
         heads = self.cfg.heads
         qkv = F.linear(x.reshape(b, side * side, c), w[p + "qkv.weight"], w[p + "qkv.bias"]).view(b, side * side, 3, heads, c // heads)
         q, k, v = qkv.unbind(2)  # strided views of the packed tensor
-        o = attention(q, k, v, scale=(c // heads) ** -0.5, rel=rel_terms(q, table_h, table_w, side), layout="bnhd")
+        if q.is_cuda and side % 2 == 0 and side <= 64:  # noqa: PLR2004 - the producer kernel reads q and the parameters in place
+            rel = sam_rel_terms(q, w[p + "rel_pos_h"], w[p + "rel_pos_w"], side)
+        else:
+            rel = rel_terms(q, table_h, table_w, side)
+        o = attention(q, k, v, scale=(c // heads) ** -0.5, rel=rel, layout="bnhd")
         return F.linear(o.view(b, side, side, c), w[p + "proj.weight"], w[p + "proj.bias"])
 
     def block(self, i: int, x: torch.Tensor) -> torch.Tensor:

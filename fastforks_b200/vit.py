@@ -1,11 +1,12 @@
 """Kernels-mode ViT encoder around the attention operator: the caller side of the hot path.
 
-A restatement of the reference's kernels-mode DINOv2 forward (`FastViT.tokens` / `FastViT.block`,
-`src/fastforks/shared/depth_anything_v2/fast_vit.py:131-180`) as a thin harness: packed qkv GEMM, attention on
-strided `[B, N, heads, 64]` views of it through `Flash64`, projection with LayerScale and residual, MLP or fused
-SwiGLU. Every non-attention op is a plain torch call (cuBLAS GEMMs, LayerNorm, GELU); the attention is the B200
-kernel. It exists to measure whole-model throughput and to check model-level parity (cosine >= 0.999 against the
-reference's portable network, `tests/golden/make_golden.py`), not to replace the reference's model zoo.
+A harness of the DINOv2 / timm ViT block family: layer norms, packed qkv, attention on strided `[B, N, heads, 64]`
+views of it through `Flash64`, projection with LayerScale and residual, MLP or fused SwiGLU. On a CUDA device every
+linear layer is one launch of this library's GEMM with the fused epilogue (bias, GELU, LayerScale, in-place residual:
+what the reference's kernels mode does with its `dpt_fused` library, `src/fastforks/shared/depth_anything_v2/
+fast_vit.py:192-208`) and the attention is the B200 kernel; LayerNorm, the patch embedding and SiLU stay torch calls.
+It exists to measure whole-model throughput and to check model-level parity (cosine >= 0.999 against the reference's
+portable network, `tests/golden/make_golden.py`), not to replace the reference's model zoo.
 
 Parameter names follow the reference's vendored DINOv2 (`net/dinov2.py`), so a state dict of that network loads here
 unchanged; `seeded_state` builds the random-init weights the benchmark configurations ask for.
@@ -20,6 +21,7 @@ import torch
 import torch.nn.functional as F  # noqa: N812
 
 from .flash64 import Flash64
+from .gemm import ACT_GELU_TANH, ACT_NONE, gemm
 
 
 @dataclass(frozen=True)
@@ -116,7 +118,8 @@ class ViTEncoder:
     """`images [B, 3, H, W]` -> normalised tokens `[B, N, dim]`, every block's attention on the B200 kernels."""
 
     def __init__(self, cfg: ViTConfig, state: dict[str, torch.Tensor], device: torch.device | str = "cuda",
-                 dtype: torch.dtype = torch.float16, variant: str = "hh") -> None:  # fmt: skip
+                 dtype: torch.dtype = torch.float16, variant: str = "hh", fused: bool | None = None,
+                 fuse_plain: bool = False) -> None:  # fmt: skip
         missing = set(state_shapes(cfg)) - set(state)
         if missing:
             msg = f"state dict lacks {sorted(missing)[:4]}..."
@@ -129,6 +132,14 @@ class ViTEncoder:
         self.pos_table = state["pos_embed"].to(self.device, torch.float32)  # interpolated in fp32, as upstream
         self.attn = Flash64(variant)
         self._pos: dict[tuple[int, int], torch.Tensor] = {}
+        # On a CUDA device the linear layers run on this library's GEMM with the fused epilogue, which takes the
+        # LayerScale factors as fp32 vectors; elsewhere (CPU harness tests) they are torch calls.
+        self.fused = self.device.type == "cuda" if fused is None else fused
+        # Layers with nothing but a bias behind the product (qkv, SwiGLU's w12) go to torch's library GEMM unless
+        # `fuse_plain`: without an epilogue to fuse there is no traffic to save, and without cluster multicast (which
+        # this library never uses) a GEMM of its own is bound by the L2 at about 0.8 of the library's rate.
+        self.fuse_plain = fuse_plain
+        self.scales = {k: v.to(self.device, torch.float32) for k, v in state.items() if k.endswith(".gamma")}
 
     def pos_embed(self, gh: int, gw: int) -> torch.Tensor:
         """Position table for a `gh x gw` patch grid (upstream `interpolate_pos_encoding`, net/dinov2.py:198-237)."""
@@ -159,25 +170,44 @@ class ViTEncoder:
         x = torch.cat([w["cls_token"].expand(b, -1, -1), x], 1)
         return x + self.pos_embed(gh, gw)
 
+    def linear(self, x: torch.Tensor, name: str, *, act: int = ACT_NONE, gamma: str | None = None,
+               residual: torch.Tensor | None = None) -> torch.Tensor:  # fmt: skip
+        """`act(x @ W^T + b)`, or with `gamma` and `residual`: `residual + gamma * (x @ W^T + b)`, written into
+        `residual`. On a CUDA device this is ONE launch of this library's GEMM with the fused epilogue
+        (`gemm`: bias, activation, LayerScale and in-place residual leave the accumulator together); elsewhere the
+        same formula in torch ops (the CPU harness tests)."""
+        w, b = self.w[name + ".weight"], self.w[name + ".bias"]
+        if self.fused and act == ACT_NONE and residual is None and not self.fuse_plain:
+            return F.linear(x, w, b)  # nothing to fuse: a plain library GEMM with bias (see `fuse_plain`)
+        if self.fused:
+            scale = self.scales[gamma] if gamma is not None else None
+            return gemm(x, w, b, act=act, scale=scale, res=residual, out=residual)
+        y = F.linear(x, w, b)
+        if act == ACT_GELU_TANH:
+            y = F.gelu(y)  # the tanh form is the fused epilogue's stand-in for this exact GELU
+        if residual is None:
+            return y
+        return residual.addcmul_(y, self.w[gamma]) if gamma is not None else residual.add_(y)
+
     def block(self, i: int, x: torch.Tensor) -> torch.Tensor:
-        """One pre-norm block, the unfused branch of `FastViT.block` (fast_vit.py:163-180)."""
+        """One pre-norm block of the DINOv2 / timm ViT family on `[B, N, C]` tokens, in place:
+        `x += ls1 * proj(attention(qkv(norm1(x))))`, `x += ls2 * ffn(norm2(x))`
+        (upstream `NestedTensorBlock.forward`, net/dinov2_layers/block.py; timm `Block.forward`,
+        src/fastforks/shared/timm_blocks/net/vit.py:60-62). q, k, v are strided views of the packed qkv tensor."""
         w, cfg, p = self.w, self.cfg, f"blocks.{i}."
         b, n, c = x.shape
-        h = cfg.heads
-        y = F.layer_norm(x, (c,), w[p + "norm1.weight"], w[p + "norm1.bias"], cfg.eps)
-        qkv = F.linear(y, w[p + "attn.qkv.weight"], w[p + "attn.qkv.bias"]).view(b, n, 3, h, c // h)
-        q, k, v = qkv.unbind(2)  # strided views of the packed tensor: nothing is copied
-        o = self.attn(q, k, v, (c // h) ** -0.5).view(b, n, c)
-        o = F.linear(o, w[p + "attn.proj.weight"], w[p + "attn.proj.bias"])
-        x = torch.addcmul(x, o, w[p + "ls1.gamma"]) if cfg.layerscale else x + o
+        heads = cfg.heads
+        ls1, ls2 = (p + "ls1.gamma", p + "ls2.gamma") if cfg.layerscale else (None, None)
+        qkv = self.linear(F.layer_norm(x, (c,), w[p + "norm1.weight"], w[p + "norm1.bias"], cfg.eps), p + "attn.qkv")
+        q, k, v = qkv.view(b, n, 3, heads, c // heads).unbind(2)
+        attended = self.attn(q, k, v, (c // heads) ** -0.5).view(b, n, c)
+        x = self.linear(attended, p + "attn.proj", gamma=ls1, residual=x)
         y = F.layer_norm(x, (c,), w[p + "norm2.weight"], w[p + "norm2.bias"], cfg.eps)
         if cfg.ffn == "swiglu":
-            x1, x2 = F.linear(y, w[p + "mlp.w12.weight"], w[p + "mlp.w12.bias"]).chunk(2, dim=-1)
-            o = F.linear(F.silu(x1) * x2, w[p + "mlp.w3.weight"], w[p + "mlp.w3.bias"])
-        else:
-            o = F.linear(F.gelu(F.linear(y, w[p + "mlp.fc1.weight"], w[p + "mlp.fc1.bias"])),
-                         w[p + "mlp.fc2.weight"], w[p + "mlp.fc2.bias"])  # fmt: skip
-        return x.addcmul_(o, w[p + "ls2.gamma"]) if cfg.layerscale else x.add_(o)
+            gate, up = self.linear(y, p + "mlp.w12").chunk(2, dim=-1)
+            return self.linear(F.silu(gate).mul_(up), p + "mlp.w3", gamma=ls2, residual=x)
+        hidden = self.linear(y, p + "mlp.fc1", act=ACT_GELU_TANH)
+        return self.linear(hidden, p + "mlp.fc2", gamma=ls2, residual=x)
 
     @torch.no_grad()
     def __call__(self, images: torch.Tensor) -> torch.Tensor:

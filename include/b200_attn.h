@@ -158,6 +158,70 @@ int b200_attn_fwd_static(const B200AttnArgs* args, void* stream);
 int b200_attn_query(const B200AttnArgs* args, int32_t* schedule);
 
 /*
+ * GEMM with a fused epilogue for the layers around attention (qkv, projection, MLP):
+ *     y[p, n] = act((sum_k x[p, k] * w[n, k] + bias[n]) * scale[n] + res[p, n])        bias, scale, res optional
+ * x is [m, k] with row stride lda, w is [n, k] row-major and contiguous, y is [m, n] with row stride ldy and may alias
+ * res (row stride lres): a LayerScale + residual block output `x += gamma * (o w^T + b)` is one call with
+ * scale = gamma, res = y = x.  x, w, bias, res, y are of `dtype`, scale is fp32, accumulation is fp32.
+ * act: 0 none, 1 relu, 5 gelu (erf), 6 gelu (tanh form).  Requirements: n, k, lda, ldy, lres multiples of 8, pointers
+ * 16-byte aligned.  It replaces `dpt_gemm(cfg, M, N, K, x, lda, w, EpiArgs*, stream)` of the reference's `dpt_fused`
+ * library (src/fastforks/kernels/dpt_fused/dpt_fused.cu:7-18, 20-34; caller `DptFused.gemm`,
+ * src/fastforks/kernels/dpt_fused/__init__.py:179-220) with the same epilogue formula, operand layouts and return
+ * codes; not carried over: the second residual / second output (res2, y2), the pixel-shuffle store of the DPT
+ * head's deconvolutions, and the tile-configuration argument (the library picks its tile itself).  bf16 is new.
+ * Launch, stream and status-word behaviour are those of b200_attn_fwd (status bits 64 / 128 / 256: the GEMM's
+ * loader, MMA issuer, epilogue).
+ */
+typedef struct B200GemmArgs {
+  uint32_t struct_size; /* sizeof(B200GemmArgs) */
+  uint32_t dtype;       /* B200_ATTN_F16 or B200_ATTN_BF16 */
+  int32_t m;
+  int32_t n;
+  int32_t k;
+  int32_t act;
+  const void* x;
+  int64_t lda;
+  const void* w;
+  const void* bias;   /* [n] or NULL */
+  const float* scale; /* [n] fp32 or NULL */
+  const void* res;    /* [m, lres] or NULL */
+  int64_t lres;
+  void* y;
+  int64_t ldy;
+} B200GemmArgs;
+
+int b200_gemm(const B200GemmArgs* args, void* stream);
+
+/*
+ * The producer of SAM's decomposed bias: for every query (y, x) of a `side` x `side` grid and k = 0 .. side - 1
+ *     rel_h[b, head, (y, x), k] = q[b, (y, x), head, :] . rel_pos_h[y - k + side - 1, :]
+ *     rel_w[b, head, (y, x), k] = q[b, (y, x), head, :] . rel_pos_w[x - k + side - 1, :]
+ * which are the `rel_h` / `rel_w` arguments of B200AttnArgs.  It replaces the two einsums of the reference's
+ * `augmented` (src/fastforks/promptable_segmentation/models/sam/fast.py:104-106) together with the table gather in
+ * front of them (`get_rel_pos`, sam/net/image_encoder.py:293-323): q is the UNSCALED query, read in place from the
+ * packed qkv tensor (element (b, n, head, d) at q + b*q_stride[0] + n*q_stride[1] + head*q_stride[2] + d, strides in
+ * elements, multiples of 8, base 16-byte aligned), `rel_pos_h` / `rel_pos_w` are the module's parameters themselves,
+ * `[2 * side - 1, 64]` contiguous, and the results are `[batch, heads, side * side, side]` contiguous, all of `dtype`.
+ * `side` must be even and at most 64 (SAM: 14 for the windows, 64 for the global blocks).
+ */
+typedef struct B200RelTermsArgs {
+  uint32_t struct_size; /* sizeof(B200RelTermsArgs) */
+  uint32_t dtype;       /* B200_ATTN_F16 or B200_ATTN_BF16 */
+  const void* q;
+  int64_t q_stride[3]; /* batch, token, head */
+  const void* rel_pos_h;
+  const void* rel_pos_w;
+  void* rel_h;
+  void* rel_w;
+  int32_t batch;
+  int32_t heads;
+  int32_t side;
+  int32_t head_dim; /* must be 64 */
+} B200RelTermsArgs;
+
+int b200_sam_rel_terms(const B200RelTermsArgs* args, void* stream);
+
+/*
  * Describes, without launching and without a GPU, the work the kernel's CTA number `cta` would do for `args` on a
  * device with `sms` SMs (148 on a B200): the grid size in *grid, the CTA's item count in *n_items, up to `max_items`
  * items as 7 integers each in `items` - batch, head, first query row, query tiles (1 or 2), first key tile, end key

@@ -231,6 +231,23 @@ def sam_encoder_case(seed: int, every: int) -> dict[str, np.ndarray]:
     return {"out": out[:, :, ::every, ::every].half(), "seed": np.int64(seed), "image_seed": np.int64(seed + 1), "every": np.int64(every)}
 
 
+def gemm_epilogue_case(seed: int) -> dict[str, np.ndarray]:
+    """The layers around attention as the reference's portable blocks compute them, in torch fp32 on the CPU:
+    `F.linear` alone (qkv), with `F.gelu` (fc1: erf form, `nn.GELU()`; and the tanh form its fused path uses on
+    full-rate cards), with `F.relu`, and `residual + gamma * F.linear(...)` (LayerScale and residual of
+    `NestedTensorBlock`, net/dinov2_layers/block.py) - the cases of the fused epilogue's formula."""
+    import torch.nn.functional as F  # noqa: N812
+
+    gen = torch.Generator().manual_seed(seed)
+    m, n, k = 70, 40, 72
+    x, w = torch.randn(m, k, generator=gen), torch.randn(n, k, generator=gen) * k**-0.5
+    bias, gamma, res = torch.randn(n, generator=gen), torch.rand(n, generator=gen) + 0.5, torch.randn(m, n, generator=gen)
+    lin = F.linear(x, w, bias)
+    return {"x": x, "w": w, "bias": bias, "scale": gamma, "res": res, "linear": lin, "gelu": F.gelu(lin),
+            "gelu_tanh": F.gelu(lin, approximate="tanh"), "relu": F.relu(lin), "layerscale_residual": res + gamma * lin,
+            "no_bias_residual": res + F.linear(x, w)}  # fmt: skip
+
+
 CASES = {
     # name: (builder, kwargs). Token counts follow the reference: 97 = its feature-golden input (112x168, patch 14),
     # 197 = ViT-B/16 at 224, 196 = one 14x14 SAM window; 8x16 exercises kh != kw.
@@ -249,6 +266,7 @@ CASES = {
     "model_dav2l_encoder_518": (dav2_encoder_case, {"seed": 11, "qk_gain": 4.0, "every": 8}),
     "model_timm_vitb16_blocks": (timm_blocks_case, {"seed": 12, "qk_gain": 4.0}),
     "model_sam_vitb_1024": (sam_encoder_case, {"seed": 13, "every": 2}),
+    "gemm_epilogue": (gemm_epilogue_case, {"seed": 14}),
 }
 
 

@@ -69,3 +69,23 @@ def test_oracle_properties() -> None:
 def test_get_rel_pos_rejects_interpolation() -> None:
     with pytest.raises(ValueError, match="interpolation"):
         ao.get_rel_pos(14, 14, np.zeros((5, 64), dtype=np.float32))
+
+
+def test_gemm_oracle_matches_the_torch_calls_of_the_portable_blocks() -> None:
+    """`oracle/gemm_oracle.py` against `tests/golden/gemm_epilogue.npz` (torch fp32 on the CPU: `F.linear`, `F.gelu`
+    in both forms, `F.relu`, LayerScale + residual): every case of the fused epilogue's formula, at fp32 round-off."""
+    from conftest import load_golden
+    from oracle import gemm_oracle as go
+
+    g = load_golden("gemm_epilogue")
+    x, w, bias, scale, res = (g[k] for k in ("x", "w", "bias", "scale", "res"))
+    cases = {
+        "linear": go.gemm_epilogue(x, w, bias),
+        "gelu": go.gemm_epilogue(x, w, bias, act=go.ACT_GELU),
+        "gelu_tanh": go.gemm_epilogue(x, w, bias, act=go.ACT_GELU_TANH),
+        "relu": go.gemm_epilogue(x, w, bias, act=go.ACT_RELU),
+        "layerscale_residual": go.gemm_epilogue(x, w, bias, scale=scale, res=res),
+        "no_bias_residual": go.gemm_epilogue(x, w, res=res),
+    }
+    for name, got in cases.items():
+        np.testing.assert_allclose(got, g[name], rtol=0, atol=3e-5, err_msg=name)

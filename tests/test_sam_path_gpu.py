@@ -9,7 +9,9 @@ restates that construction (test infrastructure: torch ops only) and
   * checks this library's `rel=(rel_h, rel_w)` call against it on the same packed qkv and tables (same operands, two
     different routes to the same logits: the bar is the path's op-level tolerance), and
   * times both, each including the two einsums that produce `rel_h`, `rel_w` from q and the tables (both routes
-    need them) and, for the reference's route, the three concatenations it needs on top.
+    need them) and, for the reference's route, the three concatenations it needs on top; and this library once more
+    with its own producer kernel (`b200_sam_rel_terms`) in place of the einsums, which is also checked against the
+    oracle on its own.
 
 Speed is reported (JSON to $B200_SAM_SIDE_BY_SIDE when set), not gated.
 """
@@ -66,6 +68,46 @@ def this_library(qkv: torch.Tensor, rh: torch.Tensor, rw: torch.Tensor, side: in
     return ff.attention(q, k, v, scale=DIM**-0.5, layout="bnhd", rel=rel_terms(qkv, rh, rw, side))
 
 
+def this_library_with_producer(qkv: torch.Tensor, pos_h: torch.Tensor, pos_w: torch.Tensor, side: int) -> torch.Tensor:
+    """The same with `rel_h`, `rel_w` from this library's producer kernel, which reads q in place and the module's
+    `[2 * side - 1, 64]` parameters instead of gathered tables."""
+    q, k, v = qkv.unbind(2)
+    return ff.attention(q, k, v, scale=DIM**-0.5, layout="bnhd", rel=ff.sam_rel_terms(q, pos_h, pos_w, side))
+
+
+def gathered(pos: torch.Tensor, side: int) -> torch.Tensor:
+    """`[side, side, 64]` table of a `[2 * side - 1, 64]` parameter (upstream `get_rel_pos`, equal sizes)."""
+    idx = torch.arange(side, device=pos.device)
+    return pos[(idx[:, None] - idx[None, :]) + (side - 1)]
+
+
+@pytest.mark.parametrize(("b", "side", "dtype"), [(25, 14, torch.float16), (1, 64, torch.float16), (3, 14, torch.bfloat16), (2, 8, torch.bfloat16), (1, 64, torch.bfloat16)])
+def test_producer_kernel_matches_the_oracle(b: int, side: int, dtype: torch.dtype) -> None:
+    """`b200_sam_rel_terms` against the oracle's restatement of the two einsums of `add_decomposed_rel_pos`
+    (oracle/attention_oracle.py: decomposed_terms) on the rounded operands; results are rounded to 16 bits once."""
+    from oracle import attention_oracle as ao
+
+    gen = torch.Generator().manual_seed(side + b)
+    qkv = torch.randn(b, side * side, 3, HEADS, DIM, generator=gen).to(dtype).cuda()
+    pos_h, pos_w = ((torch.randn(2 * side - 1, DIM, generator=gen) * 0.1).to(dtype).cuda() for _ in range(2))
+    rel_h, rel_w = ff.sam_rel_terms(qkv[:, :, 0], pos_h, pos_w, side)
+    q = qkv[:, :, 0].float().cpu().numpy().transpose(0, 2, 1, 3)
+    want_h, want_w = ao.decomposed_terms(q, pos_h.float().cpu().numpy(), pos_w.float().cpu().numpy(), (side, side))
+    assert_close(rel_h.float().cpu().numpy(), want_h, unit_scale=False, what=f"rel_h side {side} {dtype}")
+    assert_close(rel_w.float().cpu().numpy(), want_w, unit_scale=False, what=f"rel_w side {side} {dtype}")
+
+
+def test_producer_kernel_rejects_what_it_cannot_take() -> None:
+    q = torch.zeros(1, 25, 2, 64, dtype=torch.float16, device="cuda")
+    pos = torch.zeros(9, 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError, match="grid"):
+        ff.sam_rel_terms(q, pos, pos, 4)
+    with pytest.raises(ValueError, match="even"):
+        ff.sam_rel_terms(q, pos, pos, 5)
+    with pytest.raises(ValueError, match="rel_pos_h"):
+        ff.sam_rel_terms(q[:, :16], pos, pos, 4)
+
+
 def operands(b: int, side: int, seed: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     gen = torch.Generator().manual_seed(seed)
     qkv = torch.randn(b, side * side, 3, HEADS, DIM, generator=gen).half().cuda()
@@ -73,13 +115,22 @@ def operands(b: int, side: int, seed: int) -> tuple[torch.Tensor, torch.Tensor, 
     return qkv, rh, rw
 
 
+def parameters(side: int, seed: int) -> tuple[torch.Tensor, torch.Tensor]:
+    gen = torch.Generator().manual_seed(1000 + seed)
+    return tuple((torch.randn(2 * side - 1, DIM, generator=gen) * 0.1).half().cuda() for _ in range(2))
+
+
 @pytest.mark.parametrize("name", list(SHAPES))
 def test_same_result_as_the_reference_route(name: str) -> None:
     b, side = SHAPES[name]
-    qkv, rh, rw = operands(b, side, seed=side)
+    qkv, _, _ = operands(b, side, seed=side)
+    pos_h, pos_w = parameters(side, side)
+    rh, rw = gathered(pos_h, side), gathered(pos_w, side)
     theirs = reference_route(qkv, rh, rw, onehot_keys(side), side).transpose(1, 2)
     ours = this_library(qkv, rh, rw, side)
     assert_close(ours.float().cpu().numpy(), theirs.float().cpu().numpy(), unit_scale=True, what=name)
+    fused = this_library_with_producer(qkv, pos_h, pos_w, side)
+    assert_close(fused.float().cpu().numpy(), theirs.float().cpu().numpy(), unit_scale=True, what=name + " (producer kernel)")
     assert ff.device_status() == 0
 
 
@@ -110,11 +161,15 @@ def test_times_side_by_side_with_the_reference_route() -> None:
             state["i"] = (state["i"] + 1) % len(sets)
             return sets[state["i"]]
 
+        pos_h, pos_w = parameters(side, 0)
         rel_only = _time_us(lambda: rel_terms(*nxt(), side))
+        producer_only = _time_us(lambda: ff.sam_rel_terms(nxt()[0][:, :, 0], pos_h, pos_w, side))
         ours = _time_us(lambda: this_library(*nxt(), side))
+        ours_producer = _time_us(lambda: this_library_with_producer(nxt()[0], pos_h, pos_w, side))
         theirs = _time_us(lambda: reference_route(*nxt(), onehot, side))
-        rows[name] = {"rel_einsums_us": rel_only, "this_library_with_einsums_us": ours,
-                      "reference_augmented_sdpa_with_einsums_us": theirs, "speedup": theirs / ours}  # fmt: skip
+        rows[name] = {"rel_einsums_us": rel_only, "producer_kernel_us": producer_only, "this_library_with_einsums_us": ours,
+                      "this_library_with_producer_kernel_us": ours_producer,
+                      "reference_augmented_sdpa_with_einsums_us": theirs, "speedup": theirs / ours_producer}  # fmt: skip
         print(name, json.dumps(rows[name]))
     assert all(r["this_library_with_einsums_us"] > 0 for r in rows.values())
     assert ff.device_status() == 0

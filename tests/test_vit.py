@@ -81,6 +81,20 @@ def test_kernels_encoder_matches_reference_network(name: str, dtype: torch.dtype
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_kernels_encoder_with_every_linear_layer_on_the_own_gemm(dtype: torch.dtype) -> None:
+    """By default the layers with nothing to fuse behind the product (qkv) go to torch's library GEMM; with
+    `fuse_plain` all four linear layers of every block run on this library's GEMM."""
+    import fastforks_b200 as ff
+
+    g, state, images = golden_inputs("model_dinov2_vits14_sharp")
+    enc = ViTEncoder(CONFIGS["dinov2-vits14"], state, device="cuda", dtype=dtype, fuse_plain=True)
+    out = enc(images).float().cpu().numpy()
+    assert ff.device_status() == 0 and np.isfinite(out).all()
+    assert cosine(out, g["out"]) >= 0.999, cosine(out, g["out"])
+
+
+@pytest.mark.gpu
 def test_kernels_encoder_batches_are_independent() -> None:
     """Image-wise sharding relies on it: an image's output does not depend on what else is in the batch."""
     cfg = CONFIGS["dinov2-vits14"]
