@@ -61,6 +61,15 @@ CASES = {
     "vit-b16-b256": (256, 12, 197, "fp16", None),
     "vit-b16-b1": (1, 12, 197, "fp16", None),
 }
+# The other kernels of the library, for the same purpose (name -> what is launched).
+AUX_CASES = {
+    "gemm-vitl-proj": "gemm [5480,1024] x [1024,1024]^T bf16 + bias, LayerScale, in-place residual (ViT-L/14 518 px, batch 4)",
+    "gemm-vitl-fc1": "gemm [5480,1024] x [4096,1024]^T bf16 + bias, gelu (tanh form)",
+    "gemm-vitl-qkv": "gemm [5480,1024] x [3072,1024]^T bf16 + bias",
+    "gemm-4k": "gemm [4096,4096] x [4096,4096]^T bf16, no epilogue terms",
+    "sam-rel-global": "sam_rel_terms of q [1,4096,12,64] fp16, 64 x 64 grid",
+    "sam-rel-windows": "sam_rel_terms of q [25,196,12,64] fp16, 14 x 14 grid",
+}
 # DRAM bytes of one launch of the headline kernel ([8,6,1370,64] fp16): dram__bytes_read.sum + dram__bytes_write.sum
 # of one profiler capture of `python bench.py --case dinov2-vits14` (q, k, v are read once, 25.3 MB; the 8.4 MB output
 # is still in L2 when the kernel ends). A profiler figure, not something this run measures: the line says so.
@@ -546,6 +555,35 @@ def run_case(args: argparse.Namespace) -> None:
 
     import fastforks_b200 as ff
 
+    if args.case in AUX_CASES:
+        gen = torch.Generator(device="cuda").manual_seed(0)
+
+        def rnd(*shape: int, dt: torch.dtype = torch.bfloat16, mag: float = 1.0) -> torch.Tensor:
+            return (torch.randn(*shape, device="cuda", generator=gen) * mag).to(dt)
+
+        if args.case.startswith("gemm"):
+            m, n, k = {"gemm-vitl-proj": (5480, 1024, 1024), "gemm-vitl-fc1": (5480, 4096, 1024), "gemm-vitl-qkv": (5480, 3072, 1024),
+                       "gemm-4k": (4096, 4096, 4096)}[args.case]  # fmt: skip
+            x, w, bias, res = rnd(m, k), rnd(n, k, mag=k**-0.5), rnd(n), rnd(m, n)
+            scale = torch.rand(n, device="cuda", generator=gen) + 0.5
+            for _ in range(args.launches):
+                if args.case == "gemm-vitl-proj":
+                    ff.gemm(x, w, bias, scale=scale, res=res, out=res)
+                elif args.case == "gemm-vitl-fc1":
+                    ff.gemm(x, w, bias, act=ff.ACT_GELU_TANH)
+                elif args.case == "gemm-vitl-qkv":
+                    ff.gemm(x, w, bias)
+                else:
+                    ff.gemm(x, w)
+        else:
+            b, side = (1, 64) if args.case == "sam-rel-global" else (25, 14)
+            q = rnd(b, side * side, 3, 12, HEAD_DIM, dt=torch.float16)[:, :, 0]
+            pos_h, pos_w = rnd(2 * side - 1, HEAD_DIM, dt=torch.float16, mag=0.1), rnd(2 * side - 1, HEAD_DIM, dt=torch.float16, mag=0.1)
+            for _ in range(args.launches):
+                ff.sam_rel_terms(q, pos_h, pos_w, side)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": args.case, "what": AUX_CASES[args.case], "launches": args.launches, "status": ff.device_status()}))
+        return
     b, h, n, dtype, rel = CASES[args.case]
     dt = torch.float16 if dtype == "fp16" else torch.bfloat16
     gen = torch.Generator(device="cuda").manual_seed(0)
@@ -567,7 +605,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    ap.add_argument("--case", choices=tuple(CASES), default=None, help="launch one kernel case for a profiler and exit")
+    ap.add_argument("--case", choices=(*CASES, *AUX_CASES), default=None, help="launch one kernel case for a profiler and exit")
     ap.add_argument("--launches", type=int, default=4)
     ap.add_argument("--skip-partition", action="store_true", help="leave out the ViT-g/14 256-image partition leg")
     args = ap.parse_args()

@@ -218,8 +218,8 @@ def _remember(a, q, k, v, out, layout, schedule, rel=None) -> None:  # noqa: ANN
     table = getattr(_PREPARED, "table", None)
     if table is None:
         table = _PREPARED.table = {}
-    if len(table) >= _PREPARED_LIMIT:
-        table.clear()
+    while len(table) >= _PREPARED_LIMIT:  # the oldest description goes (dicts keep insertion order)
+        del table[next(iter(table))]
     copy = _lib.B200AttnArgs.from_buffer_copy(a)
     table[_geometry_key(q, k, v, layout, out, schedule, rel)] = (copy, (a.batch, a.q_tokens, a.heads, HEAD_DIM), index)
 
@@ -321,8 +321,6 @@ def attention(  # noqa: PLR0913
         a.rel_h_stride[:] = rh.stride()[:3]
         a.rel_w_stride[:] = rw.stride()[:3]
 
-    if bias is None and not keep and not _general_merge:  # no temporaries: the same geometry can be launched from the caller's pointers alone
-        _remember(a, q, k, v, given_out, layout, schedule, rel)
     index = q.device.index if q.device.index is not None else torch.cuda.current_device()
     if index != torch.cuda.current_device():
         with torch.cuda.device(index):
@@ -332,6 +330,9 @@ def attention(  # noqa: PLR0913
         _attach_workspace(a, index)
         code = lib.b200_attn_fwd(ctypes.byref(a), torch._C._cuda_getCurrentRawStream(index))  # noqa: SLF001
     _lib.raise_for_code(code, "attention")
+    if bias is None and not keep and not _general_merge:
+        # accepted, and made of the caller's own tensors only: the same geometry can be launched from pointers alone
+        _remember(a, q, k, v, given_out, layout, schedule, rel)
     for t in keep:  # the launch is asynchronous: tie temporaries to the stream
         t.record_stream(torch.cuda.current_stream(q.device))
     return out

@@ -80,33 +80,6 @@ constexpr uint64_t kOwnerPatienceNs = 30000;
 // its CTA's last item; the item's counter is the one of this CTA.
 enum : int { kItemWhole = 0, kItemPartial = 1, kItemOwner = 2 };
 
-// Development aid, compiled out of the shipped library: with -DB200_TRACE one lane per role of CTA 0 writes
-// clock stamps to AttnParams::trace so that the pipeline's timeline can be read back.
-#ifdef B200_TRACE
-// Stamps go to shared memory (one store, no divergent global access) and are copied out when the CTA leaves. They
-// borrow the bias staging area, so only the kernels without a bias can be traced.
-#define B200_STAMP(role, iter, slot)                                               \
-  do {                                                                             \
-    if (lane == 0 && (iter) < 32) {                                                \
-      uint32_t t_;                                                                 \
-      asm volatile("mov.u32 %0, %%clock;" : "=r"(t_));                             \
-      reinterpret_cast<uint32_t*>(sm.rel_stage)[((role) * 32 + (iter)) * 8 + (slot)] = t_; \
-    }                                                                              \
-  } while (0)
-// Per-CTA timeline: nanosecond marks of the first softmax warp's first lane, straight to global memory.
-#define B200_MARK(k)                                                                         \
-  do {                                                                                       \
-    if (threadIdx.x == 0 && p.trace != nullptr && (k) < 32)                                  \
-      p.trace[12 * 32 * 8 + blockIdx.x * 32 + (k)] = static_cast<long long>(global_timer_ns()); \
-  } while (0)
-#else
-#define B200_STAMP(role, iter, slot) \
-  do {                               \
-  } while (0)
-#define B200_MARK(k) \
-  do {               \
-  } while (0)
-#endif
 // Bias forms. kBiasDecomposed14 is the decomposed form specialised for a 14 x 14 key grid (SAM's windows): both
 // tables of a row sit in registers and every column's pair of indices is a compile-time constant.
 // kBiasDecomposed64 is the decomposed form specialised for rel_kw == 64, rel_kh a multiple of 8, with 16-bit, 16-byte aligned
@@ -141,7 +114,6 @@ struct AttnParams {
   int rel_staged;      // decomposed form: rel_kh + rel_kw <= 32, rows are staged in shared memory per item
   int bias_vec;        // dense form: rows are 16-byte aligned, full tiles are read with vector loads
   uint32_t* status;    // device word that collects role bits of expired waits
-  long long* trace;    // development builds only (B200_TRACE), else unused
   // Key-split mode (chunked != 0; see kPairCost). pairs_per_head = q_tiles / 2 and singles_per_head = q_tiles % 2 then.
   int chunked;
   int pair_items, single_items;  // two-tile and one-tile items of the whole problem
@@ -182,6 +154,7 @@ struct alignas(1024) AttnSmem {
   uint64_t turn[2];     // the other warpgroup is half way through its exponentials: t may start (4 warps)
   uint64_t o_staged[2];      // the item's output tile t is in o_stage[t]           (4 softmax warps)
   uint64_t o_stage_free[2];  // the TMA store of that tile has read o_stage[t]       (store thread)
+  uint64_t drain[2];         // abort path only: the MMAs query tile t's thread had in flight have finished (MMA commit)
   uint64_t merge_go[2];      // the owner's first thread has looked at the item's counter and set `merge_ready` (1)
   uint32_t merge_ready[2];   // every later part of the owner's item is counted: the owner folds them in itself
   uint32_t o_store[2][2];    // [t][item parity] what the hand-over o_staged[t] of a cut item means: 1 a staged tile, 2 a part in the workspace
@@ -516,7 +489,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  B200_MARK(0);
 
   const int kv_tiles = p.kv_tiles;
   // Keys of the last tile, rounded up to the MMA granule: its S needs no more columns, its P V no more steps.
@@ -539,6 +511,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&sm.o_staged[i], 4);
       mbar_init(&sm.o_stage_free[i], 1);
       mbar_init(&sm.merge_go[i], 1);
+      mbar_init(&sm.drain[i], 1);
     }
     for (int i = 0; i < kStagesK; ++i) {
       mbar_init(&sm.k_full[i], 1);
@@ -550,9 +523,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     sm.abort = 0;
     sm.work = cta_work(p, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
-#ifdef B200_TRACE
-    for (int i = 0; i < 12 * 32 * 8; ++i) reinterpret_cast<uint32_t*>(sm.rel_stage)[i] = 0;
-#endif
     mbar_init_fence();
   }
   if (warp == kMmaWarp) {
@@ -573,7 +543,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // below reads or writes global memory and waits here until the earlier kernel has completed and its writes are
   // visible. Without an earlier kernel, or without the launch attribute, the wait returns at once.
   grid_dependency_wait();
-  B200_MARK(1);
   const uint32_t tmem = sm.tmem_base;
   volatile uint32_t* abort_flag = &sm.abort;
   const CtaWork& cw = sm.work;
@@ -700,7 +669,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (x.gs > 0 && !mbar_wait(s_free, (x.gs - 1) & 1, abort_flag)) return false;  // S_t has been read
           if (!k_early && !mbar_wait(&sm.k_full[x.st], x.ph, abort_flag)) return false;
           tc_fence_after_sync();
-          B200_STAMP(2 + t, x.gs, 2);
           const uint64_t a = q_desc0 + static_cast<uint64_t>(slot) * kStageStep;
           const uint64_t bd = k_desc0 + static_cast<uint64_t>(x.st) * kStageStep;
           const uint32_t idesc = (x.j == kv_tiles - 1) ? idesc_qk_last : idesc_qk;
@@ -711,7 +679,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           umma_commit(&sm.k_empty[x.st]);
           if (x.it >= my_doubles) umma_commit(&sm.k_empty[x.st]);  // one-tile item: stand in for the absent second tile
           if (is_last(x)) umma_commit(&sm.q_empty[t][slot]);  // the item's last reader of Q_t
-          B200_STAMP(2 + t, x.gs, 3);
           return true;
         };
         // O_t (+)= P_t(gs) V, 16 keys (two 8-row groups of the V tile) per MMA.
@@ -722,7 +689,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // The first P V of an item overwrites O_t: the previous item's epilogue must have read it.
           if (is_first(x) && x.it > 0 && !mbar_wait(&sm.o_free[t], (x.it - 1) & 1, abort_flag)) return false;
           tc_fence_after_sync();
-          B200_STAMP(2 + t, x.gs, 0);
           const uint64_t bd = v_desc0 + static_cast<uint64_t>(x.st) * kStageStep;
           if (x.j != kv_tiles - 1) {
             umma_ts(o_tm, p_tm, bd, idesc_pv, is_first(x) ? 0u : 1u);
@@ -739,7 +705,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           umma_commit(pv_done);
           umma_commit(&sm.v_empty[x.st]);
           if (x.it >= my_doubles) umma_commit(&sm.v_empty[x.st]);
-          B200_STAMP(2 + t, x.gs, 1);
           return true;
         };
 
@@ -757,6 +722,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         if (!ok) {
           if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusMma);
+        }
+        if (*abort_flag != 0) {
+          // Some role gave up: products this thread issued may still be running, and their commits must not
+          // arrive on barriers of a CTA that is gone (nor tensor memory be freed under them). One last commit on
+          // a barrier of its own, waited for with the usual limit and without looking at the abort flag.
+          uint32_t no_abort = 0;
+          umma_commit(&sm.drain[t]);
+          mbar_wait(&sm.drain[t], 0, &no_abort);
         }
       }
       __syncwarp();
@@ -872,7 +845,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // loop finish an item that has a successor): the owner's code is compiled into that one call only.
     auto finish_item = [&](bool pv_tested, bool stage_tested, auto at_end) -> bool {
       [[maybe_unused]] constexpr bool kAtEnd = decltype(at_end)::value;
-      B200_MARK(12 + 2 * pend_it);
       if (!__all_sync(0xffffffffu, pv_tested || mbar_wait(&sm.pv_done[t], pend_phase, abort_flag))) return false;
       tc_fence_after_sync();
       float o[kHeadDim];
@@ -952,7 +924,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 !__all_sync(0xffffffffu, stage_tested || mbar_wait(&sm.o_stage_free[t], (pend_it - 1) & 1, abort_flag)))
               return false;
             warp_arrive(&sm.o_staged[t], lane);
-            B200_MARK(13 + 2 * pend_it);
             pend = false;
             return true;
           }
@@ -975,7 +946,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       fence_proxy_async_smem();  // the TMA store reads what these generic-proxy stores wrote
       warp_arrive(&sm.o_staged[t], lane);
-      B200_MARK(13 + 2 * pend_it);
       pend = false;
       return true;
     };
@@ -1069,8 +1039,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         bad |= !mbar_wait_warp_after(s_early, &sm.s_full[t], step & 1, abort_flag);
         tc_fence_after_sync();
-        if (step == 0) B200_MARK(2);
-        if ((warp & 3) == 0) B200_STAMP(t, step, 0);
 
         float s[kTileRows];
         {
@@ -1085,7 +1053,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // S_t is in registers: the tensor pipe may overwrite it with the tile after next.
         tc_fence_before_sync();
         warp_arrive(&sm.s_free[t], lane);
-        if ((warp & 3) == 0) B200_STAMP(t, step, 1);
         // Tests of the barriers this step will wait on, issued here so that their latency (100-150 clocks each with
         // tensor memory allocated) runs behind the arithmetic; a test that finds its phase pending is repeated as a
         // real wait where the result is needed.
@@ -1248,7 +1215,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         l_sum *= alpha;
         const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-        if ((warp & 3) == 0) B200_STAMP(t, step, 6);
 
         // ---- exponentials ---------------------------------------------------------------------------
         // Both warpgroups feed the MUFU unit, but they must not run in lockstep (their loads and reductions
@@ -1257,7 +1223,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // step q+1 after warpgroup 1's midpoint of step q, warpgroup 1 starts step q after warpgroup 0's
         // midpoint of step q. Half a section apart, neither ever waits here.
         if (need_turn) bad |= !mbar_wait_warp_after(turn_early, &sm.turn[t], turn_parity, abort_flag);
-        if ((warp & 3) == 0) B200_STAMP(t, step, 2);
         float2 l2a = make_float2(0.f, 0.f), l2b = make_float2(0.f, 0.f);
         const float2 c2 = (BIAS == kBiasNone)           ? make_float2(c, c)
                           : (BIAS == kBiasDecomposed64) ? make_float2(kLog2e, kLog2e)
@@ -1311,7 +1276,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         } else {
           exp_columns(integral_constant<int, 2>{}, integral_constant<int, 2>{});
         }
-        if ((warp & 3) == 0) B200_STAMP(t, step, 3);
         l_sum += (l2a.x + l2a.y) + (l2b.x + l2b.y);
 
         // P_t and O_t may only change once P_t(j-1) V has finished: it was issued when this warpgroup
@@ -1336,13 +1300,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tmem_st_x32(o_addr + 32, ou + 32);
           }
         }
-        if ((warp & 3) == 0) B200_STAMP(t, step, 4);
         tmem_st_x32(p_addr, pk);
         tmem_st_x32(p_addr + 32, pk + 32);
         tmem_st_wait();
         tc_fence_before_sync();
         warp_arrive(&sm.p_full[t], lane);
-        if ((warp & 3) == 0) B200_STAMP(t, step, 5);
       }
       if (!ok) break;
       if (__any_sync(0xffffffffu, bad)) {
@@ -1350,7 +1312,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         break;
       }
 
-      B200_MARK(3 + it);
       // The item's output is written later (see above); remember what its epilogue needs.
       pend = true;
       pend_phase = (g + (jb - ja) - 1) & 1;
@@ -1369,11 +1330,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // ---- common exit ----------------------------------------------------------------------------
   tc_fence_before_sync();
   __syncthreads();
-  B200_MARK(31);
-#ifdef B200_TRACE
-  if (blockIdx.x == 0 && p.trace != nullptr)
-    for (int i = threadIdx.x; i < 12 * 32 * 8; i += kThreads) p.trace[i] = reinterpret_cast<uint32_t*>(sm.rel_stage)[i];
-#endif
   if (warp == kMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kTmemCols);

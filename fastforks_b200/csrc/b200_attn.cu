@@ -46,9 +46,6 @@ uint64_t div_magic(int d) { return d <= 1 ? 0 : ~uint64_t(0) / static_cast<uint6
 
 thread_local char tl_error[512] = "";
 
-#ifdef B200_TRACE
-long long* g_trace_buffer = nullptr;  // development builds only
-#endif
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -100,6 +97,48 @@ int make_tile_map(CUtensorMap* map, const void* base, uint32_t dtype, int batch,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(B200_ATTN_UNSUPPORTED, "tensor map for %s rejected by the driver (CUresult %d)", name, static_cast<int>(r));
+  return B200_ATTN_OK;
+}
+
+// Tensor maps made before, per thread: a model calls the operator with the same views (and, through torch's
+// caching allocator, the same addresses) in every block and every forward, and for launch-bound shapes (one image of
+// 197 tokens) four calls of the driver's encoder cost more host time than the rest of the launch. A map depends on
+// nothing but the key, so a hit is exact; the oldest entry of a slot's set goes on a miss.
+struct TileMapKey {
+  const void* base;
+  int64_t stride[3];
+  int batch, heads, tokens;
+  uint32_t dtype;
+  bool operator==(const TileMapKey& o) const {
+    return base == o.base && stride[0] == o.stride[0] && stride[1] == o.stride[1] && stride[2] == o.stride[2] && batch == o.batch &&
+           heads == o.heads && tokens == o.tokens && dtype == o.dtype;
+  }
+};
+constexpr int kTileMapSets = 64, kTileMapWays = 2;
+struct TileMapCache {
+  TileMapKey key[kTileMapSets][kTileMapWays];
+  CUtensorMap map[kTileMapSets][kTileMapWays];
+  bool used[kTileMapSets][kTileMapWays];
+  uint8_t next[kTileMapSets];
+};
+thread_local TileMapCache tl_tile_maps{};
+
+int cached_tile_map(CUtensorMap* map, const void* base, uint32_t dtype, int batch, int heads, int tokens, const int64_t stride[3],
+                    const char* name) {
+  const TileMapKey key{base, {stride[0], stride[1], stride[2]}, batch, heads, tokens, dtype};
+  const size_t h = (reinterpret_cast<uintptr_t>(base) >> 8) * 0x9E3779B97F4A7C15ull >> 58;  // 6 bits
+  TileMapCache& c = tl_tile_maps;
+  for (int w = 0; w < kTileMapWays; ++w)
+    if (c.used[h][w] && c.key[h][w] == key) {
+      *map = c.map[h][w];
+      return B200_ATTN_OK;
+    }
+  if (const int rc = make_tile_map(map, base, dtype, batch, heads, tokens, stride, name)) return rc;
+  const int w = c.next[h];
+  c.next[h] = static_cast<uint8_t>((w + 1) % kTileMapWays);
+  c.key[h][w] = key;
+  c.map[h][w] = *map;
+  c.used[h][w] = true;
   return B200_ATTN_OK;
 }
 
@@ -415,10 +454,10 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
 
   CUtensorMap mq, mk, mv, mo;
-  if ((rc = make_tile_map(&mq, a->q, a->dtype, a->batch, a->heads, a->q_tokens, a->q_stride, "q"))) return rc;
-  if ((rc = make_tile_map(&mk, a->k, a->dtype, a->batch, a->heads, a->kv_tokens, a->k_stride, "k"))) return rc;
-  if ((rc = make_tile_map(&mv, a->v, a->dtype, a->batch, a->heads, a->kv_tokens, a->v_stride, "v"))) return rc;
-  if ((rc = make_tile_map(&mo, a->o, a->dtype, a->batch, a->heads, a->q_tokens, a->o_stride, "o"))) return rc;
+  if ((rc = cached_tile_map(&mq, a->q, a->dtype, a->batch, a->heads, a->q_tokens, a->q_stride, "q"))) return rc;
+  if ((rc = cached_tile_map(&mk, a->k, a->dtype, a->batch, a->heads, a->kv_tokens, a->k_stride, "k"))) return rc;
+  if ((rc = cached_tile_map(&mv, a->v, a->dtype, a->batch, a->heads, a->kv_tokens, a->v_stride, "v"))) return rc;
+  if ((rc = cached_tile_map(&mo, a->o, a->dtype, a->batch, a->heads, a->q_tokens, a->o_stride, "o"))) return rc;
 
   AttnParams prm;
   std::memset(&prm, 0, sizeof(prm));
@@ -463,9 +502,6 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
   if ((rc = device_state(&dev))) return rc;
   prm.status = dev->status;
 
-#ifdef B200_TRACE
-  prm.trace = g_trace_buffer;
-#endif
   const unsigned grid = plan_work(prm, a, dev->sms);
   const bool f16 = a->dtype == B200_ATTN_F16;
   const bool short_sched = sched == B200_ATTN_SCHED_SHORT;
@@ -733,17 +769,6 @@ int b200_attn_status(uint32_t* status) {
   return B200_ATTN_OK;
 }
 
-#ifdef B200_TRACE
-void b200_attn_debug_set_trace(void* device_buffer) { g_trace_buffer = static_cast<long long*>(device_buffer); }
-int b200_attn_debug_timeouts(unsigned int* out /* [256][4] */) {
-  unsigned int n = 0, zero = 0;
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(&n, b200::g_dbg_count, sizeof(n));
-  cudaMemcpyFromSymbol(out, b200::g_dbg, sizeof(unsigned int) * 256 * 4);
-  cudaMemcpyToSymbol(b200::g_dbg_count, &zero, sizeof(zero));
-  return static_cast<int>(n);
-}
-#endif
 
 int b200_attn_selftest_wait_limit(uint32_t limit_us, void* stream_ptr) {
   if (limit_us == 0 || limit_us > 100000)

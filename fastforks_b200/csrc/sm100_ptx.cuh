@@ -90,17 +90,6 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 // when another thread of the CTA has already raised `*abort_flag` (shared memory).
 // The wall clock is only consulted after a long run of failed polls (each try_wait already sleeps in
 // hardware for a while), so a wait that succeeds quickly costs a handful of instructions.
-#ifdef B200_TRACE
-__device__ unsigned int g_dbg_count;
-__device__ unsigned int g_dbg[256][4];
-__device__ __forceinline__ void dbg_timeout(uint64_t* bar, uint32_t parity, int why) {
-  const unsigned int i = atomicAdd(&g_dbg_count, 1u);
-  if (i < 256) { g_dbg[i][0] = blockIdx.x; g_dbg[i][1] = threadIdx.x; g_dbg[i][2] = smem_u32(bar); g_dbg[i][3] = parity | (why << 8); }
-}
-#define B200_DBG_TIMEOUT(bar, parity, why) dbg_timeout(bar, parity, why)
-#else
-#define B200_DBG_TIMEOUT(bar, parity, why) do {} while (0)
-#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
 #pragma unroll 1
   for (uint32_t polls = 0; polls < 4096; ++polls)
@@ -110,8 +99,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++polls & 0xff) == 0) {
-      if (*abort_flag != 0) { B200_DBG_TIMEOUT(bar, parity, 2); return false; }
-      if (global_timer_ns() - t0 > B200_WAIT_LIMIT_NS) { B200_DBG_TIMEOUT(bar, parity, 1); return false; }
+      if (*abort_flag != 0) return false;
+      if (global_timer_ns() - t0 > B200_WAIT_LIMIT_NS) return false;
     }
   }
 }

@@ -1,22 +1,22 @@
 """Typed errors of the B200 attention backend.
 
-Same names and meaning as the reference's `src/fastforks/_core/errors.py:40-60`: asking for the kernels
-backend where it cannot run raises, it never falls back silently.
+The class names and their meaning are the reference's (`src/fastforks/_core/errors.py:40-66`), so code written
+against it catches the same things: the kernels backend either runs or raises, it never quietly does something else.
 """
 
 from __future__ import annotations
 
 
 class BackendUnavailableError(RuntimeError):
-    """The requested backend (`mode="kernels"`) cannot run here. There is no silent fallback."""
+    """Raised when a backend was asked for by name (`mode="kernels"`) on a machine where it cannot run."""
 
 
 class KernelUnavailableError(BackendUnavailableError):
-    """The kernel library cannot be loaded on this machine.
+    """Raised when the compiled kernel library is missing, stale or does not load.
 
     Attributes:
-        library: Kernel library name.
-        reason: Why it cannot be loaded (no binary, no GPU, wrong architecture, ...).
+        library: Which library (`"b200attn"`).
+        reason: What is wrong with it and, where there is one, the command that fixes it.
     """
 
     def __init__(self, library: str, reason: str) -> None:

@@ -24,36 +24,42 @@ FLASH_PROBE = 64
 
 
 def check_flash64(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor | None = None) -> None:
-    """Check the launch contract: same-shape fp16 / bf16 CUDA `[B, N, heads, 64]` views with unit last stride.
+    """What `Flash64` accepts, checked before anything is launched: q, k, v (and o, if given) of one shape
+    `[B, N, heads, 64]`, fp16 or bf16, on one CUDA device, last dimension contiguous.
 
     Raises:
-        ValueError: A dtype, head dim, shape, device or stride the kernel cannot read.
+        ValueError: An operand breaks one of these rules; the message names it.
     """
     check_operands(q, k, v, "bnhd", o)
     if k.shape != q.shape:
-        msg = f"flash64: q, k, v, o shapes differ: {[tuple(t.shape) for t in (q, k, v)]}"
+        msg = f"flash64: self-attention only, but q is {tuple(q.shape)} and k / v are {tuple(k.shape)}"
         raise ValueError(msg)
 
 
+def _known_variant(variant: str) -> str:
+    if variant not in FLASH_VARIANTS:
+        msg = f"flash64: variant {variant!r} is not one of {', '.join(FLASH_VARIANTS)}"
+        raise ValueError(msg)
+    return variant
+
+
 class Flash64:
-    """Attention of one model over `[B, N, heads, 64]` views (see the module docstring)."""
+    """A model's attention launcher with the reference's interface (see the module docstring). The attributes
+    `variant`, `probe` and `window` exist because callers and tests of the reference read them; only `variant` is
+    ever looked at here, and every variant runs the same kernel."""
 
     def __init__(self, variant: str = "hh", *, probe: int = FLASH_PROBE) -> None:
-        """`variant`: one of `FLASH_VARIANTS`; `probe`: kept for compatibility, nothing is probed."""
-        if variant not in FLASH_VARIANTS:
-            msg = f"flash64 variant {variant!r}: expected one of {FLASH_VARIANTS}"
-            raise ValueError(msg)
-        self.variant, self.probe, self.window = variant, probe, probe
+        self.variant = _known_variant(variant)
+        self.probe = self.window = probe  # no overflow probe is needed with fp32 accumulation; kept for the interface
 
     def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
-        """softmax(q k^T * scale) v of `[B, N, heads, 64]` views (unit last stride) -> new `[B, N, heads, 64]`."""
+        """Attention of strided `[B, N, heads, 64]` views; the result is a new contiguous tensor of that shape."""
         return self._run(self.variant, q, k, v, scale)
 
     @staticmethod
     def _run(variant: str, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
-        if variant not in FLASH_VARIANTS:
-            msg = f"flash64 variant {variant!r}: expected one of {FLASH_VARIANTS}"
-            raise ValueError(msg)
+        """The one place a launch happens (the reference's tests replace this method to observe launches)."""
+        _known_variant(variant)
         check_flash64(q, k, v)
         b, n, h, _ = q.shape
         o = torch.empty((b, n, h, HEAD_DIM), device=q.device, dtype=q.dtype)

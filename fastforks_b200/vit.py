@@ -217,6 +217,23 @@ class ViTEncoder:
         c = x.shape[-1]
         return F.layer_norm(x, (c,), self.w["norm.weight"], self.w["norm.bias"], self.cfg.eps)
 
+    def checked(self, images: torch.Tensor) -> torch.Tensor:
+        """`self(images)`, then one read of the device's error word (one synchronisation per model call, like the
+        reference's `kernels.checked`): every wait inside the kernels is bounded, and a kernel that gave one up
+        returns normally with an invalid output, which only this word shows.
+
+        Raises:
+            RuntimeError: A kernel of this call gave up a wait; the output must not be used.
+        """
+        from .attention import device_status
+
+        out = self(images)
+        status = device_status(self.device)
+        if status != 0:
+            msg = f"a kernel gave up a bounded wait during this call (status word {status}); the output is invalid"
+            raise RuntimeError(msg)
+        return out
+
     @torch.no_grad()
     def intermediate(self, images: torch.Tensor, layers: tuple[int, ...]) -> list[torch.Tensor]:
         """Normalised tokens after the blocks in `layers`: what the depth models hand to their DPT head

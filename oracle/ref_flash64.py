@@ -19,11 +19,14 @@ SHARED_OBJECT = HERE / "_ref" / "libref_flash64.so"
 VARIANTS = {"hh": 0, "fh": 1, "ff": 2}
 
 
-def build(reference: str = "/root/reference") -> Path | None:
-    """Compile the library when the reference checkout is present; return its path, or None when it cannot be built
-    and no earlier build exists."""
+def build(reference: str | None = None) -> Path | None:
+    """Compile the library from the reference checkout at `reference` (default: the environment variable
+    `FASTFORKS_REFERENCE`); return its path, or None when there is no checkout and no earlier build exists."""
+    import os
+
+    reference = reference or os.environ.get("FASTFORKS_REFERENCE", "")
     src = Path(reference) / "src/fastforks/kernels/fastbb/fastbb_kernels.cu"
-    if src.exists():
+    if reference and src.exists():
         subprocess.run(["make", "-C", str(HERE), f"REFERENCE={reference}", "_ref"], check=True, capture_output=True)
     return SHARED_OBJECT if SHARED_OBJECT.exists() else None
 
