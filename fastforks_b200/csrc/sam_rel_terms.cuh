@@ -87,7 +87,26 @@ __global__ void __launch_bounds__(kRelThreads) sam_rel_terms_kernel(const RelTer
       }
     }
     T* dst = out + ((static_cast<int64_t>(b) * p.heads + head) * n_tokens + n) * side;
-    for (int k = 0; k < side; k += 2) {  // side is even (checked by the host): two results per 32-bit store
+    // side is even (checked by the host). Four table rows at a time where they exist: four independent chains of
+    // fused multiply-adds hide the latency of the shared-memory loads behind them; a leftover pair goes alone.
+    int k = 0;
+    for (; k + 4 <= side; k += 4) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ch = 0; ch < 64; ch += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float4 t = *reinterpret_cast<const float4*>(&table[k + u][ch]);
+          acc[u] = fmaf(q[ch], t.x, acc[u]);
+          acc[u] = fmaf(q[ch + 1], t.y, acc[u]);
+          acc[u] = fmaf(q[ch + 2], t.z, acc[u]);
+          acc[u] = fmaf(q[ch + 3], t.w, acc[u]);
+        }
+      }
+      *reinterpret_cast<uint32_t*>(dst + k) = rel_pack2<T>(acc[0], acc[1]);
+      *reinterpret_cast<uint32_t*>(dst + k + 2) = rel_pack2<T>(acc[2], acc[3]);
+    }
+    for (; k < side; k += 2) {
       float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
       for (int ch = 0; ch < 64; ch += 4) {
