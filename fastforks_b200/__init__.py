@@ -13,7 +13,7 @@ import logging
 
 from . import _lib
 from ._lib import build
-from .attention import attention, check_operands, device_status, reserve_workspace
+from .attention import attention, check_operands, device_status, reserve_workspace, tile_layout
 from .errors import BackendUnavailableError, KernelUnavailableError
 from .gemm import ACT_GELU, ACT_GELU_TANH, ACT_NONE, ACT_RELU, gemm
 from .flash64 import FLASH_VARIANTS, Flash64, check_flash64
@@ -41,6 +41,7 @@ __all__ = [
     "reserve_workspace",
     "resolve_mode",
     "sam_rel_terms",
+    "tile_layout",
     "scaled_dot_product_attention",
     "version",
 ]

@@ -90,9 +90,45 @@ def check_operands(
         raise ValueError(msg)
 
 
-def _bias_view(name: str, t: torch.Tensor, shape: Sequence[int], q: torch.Tensor) -> tuple[torch.Tensor, bool]:
+def _tile_layout(t: torch.Tensor) -> bool:
+    """Whether the kernel can fetch the 4-D bias `t` as tiles: 16-bit, 16-byte aligned base, rows and (where they are
+    not broadcast) batch and head strides in multiples of 8 elements."""
+    if t.dtype not in (torch.float16, torch.bfloat16) or t.data_ptr() % 16 or t.stride(3) != 1:
+        return False
+    sb, sh, sn, _ = (0 if extent == 1 else stride for extent, stride in zip(t.shape, t.stride(), strict=True))
+    return sn % 8 == 0 and sb % 8 == 0 and sh % 8 == 0 and (sn > 0 or t.shape[2] == 1)
+
+
+def tile_layout(bias: torch.Tensor) -> torch.Tensor:
+    """A 16-bit additive bias `[B | 1, heads | 1, N, Nk]` (fewer leading dims allowed) as a view of the same values
+    whose rows begin on 16-byte boundaries: a copy into rows padded to a multiple of 8 columns unless `bias` has that
+    layout already.
+
+    The kernel brings such a bias in through the tensor memory accelerator, tile by tile like K and V; any other
+    layout is read row by row, several times slower. `attention` makes this copy itself on every call that needs
+    it; a caller with a constant bias (a relative-position table per block, a window mask) converts it once.
+    """
+    t = bias
+    while t.dim() < 4:  # noqa: PLR2004
+        t = t.unsqueeze(0)
+    if t.dtype not in (torch.float16, torch.bfloat16):
+        msg = f"tile_layout: a float16 / bfloat16 bias is needed, got {t.dtype}"
+        raise ValueError(msg)
+    if _tile_layout(t):
+        return t
+    nk = t.shape[3]
+    wide = torch.empty((*t.shape[:3], (nk + 7) // 8 * 8), dtype=t.dtype, device=t.device)
+    out = wide[..., :nk]
+    out.copy_(t)
+    return out
+
+
+def _bias_view(
+    name: str, t: torch.Tensor, shape: Sequence[int], q: torch.Tensor, *, tiled: bool = False
+) -> tuple[torch.Tensor, bool]:
     """`t` as a view broadcast to 4-D `shape` with unit last stride, and whether a copy had to be made for it
-    (only if its last stride is not 1 or its last two dims must be materialised)."""
+    (only if its last stride is not 1, its last two dims must be materialised, or, with `tiled`, a 16-bit bias
+    does not have the layout of `tile_layout`)."""
     source = t
     if t.dtype not in _BIAS_DTYPES or t.device != q.device:
         msg = f"attention: {name} must be float16 / bfloat16 / float32 on {q.device}, got {t.dtype} on {t.device}"
@@ -109,6 +145,8 @@ def _bias_view(name: str, t: torch.Tensor, shape: Sequence[int], q: torch.Tensor
         t = t.expand(t.shape[0], t.shape[1], shape[-2], shape[-1]).contiguous()
     if t.stride(-1) != 1:
         t = t.contiguous()
+    if tiled and t.dtype != torch.float32 and not _tile_layout(t):
+        t = tile_layout(t)
     copied = t.untyped_storage().data_ptr() != source.untyped_storage().data_ptr()
     try:
         return t.expand(*shape), copied
@@ -171,22 +209,23 @@ _PREPARED = threading.local()
 _PREPARED_LIMIT = 256
 
 
-def _geometry_key(q, k, v, layout, out, schedule, rel=None):  # noqa: ANN001, ANN202, PLR0913
+def _geometry_key(q, k, v, layout, out, schedule, rel=None, bias=None):  # noqa: ANN001, ANN202, PLR0913
     return (
         q.dtype, k.dtype, v.dtype, q.device, k.device, v.device, layout, schedule, q.shape, k.shape, v.shape,
         q.stride(), k.stride(), v.stride(),
         None if out is None else (out.dtype, out.device, out.shape, out.stride()),
         None if rel is None else tuple((t.dtype, t.device, t.shape, t.stride()) for t in rel),
+        None if bias is None else (bias.dtype, bias.device, bias.shape, bias.stride(), bias.data_ptr() % 16),
     )  # fmt: skip
 
 
-def _launch_prepared(q, k, v, scale, layout, out, schedule, rel=None):  # noqa: ANN001, ANN202, PLR0913
+def _launch_prepared(q, k, v, scale, layout, out, schedule, rel=None, bias=None):  # noqa: ANN001, ANN202, PLR0913
     """Launch from a remembered description of this geometry; None when there is none (the full path then runs)."""
     table = getattr(_PREPARED, "table", None)
     if table is None:
         return None
     try:
-        entry = table.get(_geometry_key(q, k, v, layout, out, schedule, rel))
+        entry = table.get(_geometry_key(q, k, v, layout, out, schedule, rel, bias))
     except (AttributeError, TypeError, ValueError):  # not tensors: let the full path raise its ValueError
         return None
     if entry is None:
@@ -202,6 +241,8 @@ def _launch_prepared(q, k, v, scale, layout, out, schedule, rel=None):  # noqa: 
     a.q, a.k, a.v, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
     if rel is not None:  # remembered only where the tables went in as they are (broadcast views of the same memory)
         a.rel_h, a.rel_w = rel[0].data_ptr(), rel[1].data_ptr()
+    if bias is not None:  # likewise
+        a.bias = bias.data_ptr()
     a.scale = float(HEAD_DIM**-0.5 if scale is None else scale)
     _attach_workspace(a, index)
     code = _lib.library().b200_attn_fwd(ctypes.byref(a), torch._C._cuda_getCurrentRawStream(index))  # noqa: SLF001
@@ -210,7 +251,7 @@ def _launch_prepared(q, k, v, scale, layout, out, schedule, rel=None):  # noqa: 
     return out
 
 
-def _remember(a, q, k, v, out, layout, schedule, rel=None) -> None:  # noqa: ANN001, PLR0913
+def _remember(a, q, k, v, out, layout, schedule, rel=None, bias=None) -> None:  # noqa: ANN001, PLR0913
     """Keep the checked description `a` of this geometry for the calling thread (`out` as the caller gave it)."""
     index = q.device.index
     if index is None or index != torch.cuda.current_device():
@@ -221,7 +262,7 @@ def _remember(a, q, k, v, out, layout, schedule, rel=None) -> None:  # noqa: ANN
     while len(table) >= _PREPARED_LIMIT:  # the oldest description goes (dicts keep insertion order)
         del table[next(iter(table))]
     copy = _lib.B200AttnArgs.from_buffer_copy(a)
-    table[_geometry_key(q, k, v, layout, out, schedule, rel)] = (copy, (a.batch, a.q_tokens, a.heads, HEAD_DIM), index)
+    table[_geometry_key(q, k, v, layout, out, schedule, rel, bias)] = (copy, (a.batch, a.q_tokens, a.heads, HEAD_DIM), index)
 
 
 def attention(  # noqa: PLR0913
@@ -236,6 +277,7 @@ def attention(  # noqa: PLR0913
     out: torch.Tensor | None = None,
     schedule: str = "auto",
     _general_merge: bool = False,
+    _bias_as_given: bool = False,
 ) -> torch.Tensor:
     """`softmax(scale * q k^T + bias) v` on the B200 kernels; q, k, v are views, nothing is copied.
 
@@ -245,7 +287,9 @@ def attention(  # noqa: PLR0913
         k: Same layout as q, `[.., Nk, ..]`.
         v: Same shape as k.
         scale: Softmax scale; default `64 ** -0.5` as in SDPA and the reference's modules.
-        bias: Additive float bias broadcastable to `[B, heads, N, Nk]` (an SDPA float `attn_mask`).
+        bias: Additive float bias broadcastable to `[B, heads, N, Nk]` (an SDPA float `attn_mask`). A 16-bit bias
+            is fetched in tiles; if its rows do not begin on 16-byte boundaries it is first copied into rows that do
+            (`tile_layout`: do that once for a constant bias). A float32 bias is read row by row, much slower.
         rel: SAM's decomposed relative-position term `(rel_h [B, heads, N, kh], rel_w [B, heads, N, kw])` with
             `kh * kw == Nk`: `bias[i, j] = rel_h[i, j // kw] + rel_w[i, j % kw]`
             (`src/fastforks/promptable_segmentation/models/sam/net/image_encoder.py:326-362`), never materialised.
@@ -263,8 +307,8 @@ def attention(  # noqa: PLR0913
         KernelUnavailableError: The CUDA library is not built or does not load.
         RuntimeError: A CUDA error at launch.
     """
-    if bias is None and not _general_merge:
-        done = _launch_prepared(q, k, v, scale, layout, out, schedule, rel)
+    if not _general_merge and not _bias_as_given:
+        done = _launch_prepared(q, k, v, scale, layout, out, schedule, rel, bias)
         if done is not None:
             return done
     check_operands(q, k, v, layout, out)
@@ -300,7 +344,7 @@ def attention(  # noqa: PLR0913
         if bias.dtype == torch.bool:  # SDPA: True = takes part in attention
             bias = torch.zeros_like(bias, dtype=q.dtype).masked_fill_(~bias, float("-inf"))
         made = bias.dtype != given_bias_dtype
-        bv, copied = _bias_view("bias", bias, (b, h, n, nk), q)
+        bv, copied = _bias_view("bias", bias, (b, h, n, nk), q, tiled=not _bias_as_given)
         if made or copied:
             keep.append(bv)
         a.bias, a.bias_dtype = bv.data_ptr(), _BIAS_DTYPES[bv.dtype]
@@ -330,9 +374,9 @@ def attention(  # noqa: PLR0913
         _attach_workspace(a, index)
         code = lib.b200_attn_fwd(ctypes.byref(a), torch._C._cuda_getCurrentRawStream(index))  # noqa: SLF001
     _lib.raise_for_code(code, "attention")
-    if bias is None and not keep and not _general_merge:
+    if not keep and not _general_merge and not _bias_as_given:
         # accepted, and made of the caller's own tensors only: the same geometry can be launched from pointers alone
-        _remember(a, q, k, v, given_out, layout, schedule, rel)
+        _remember(a, q, k, v, given_out, layout, schedule, rel, bias)
     for t in keep:  # the launch is asynchronous: tie temporaries to the stream
         t.record_stream(torch.cuda.current_stream(q.device))
     return out

@@ -24,6 +24,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstddef>
 #include <type_traits>
 
 #include "sm100_ptx.cuh"
@@ -43,7 +44,8 @@ constexpr int kLaunchRegs = 168;                      // what a 384-thread CTA g
 // allocated, or the second warpgroup waits for ever.
 static_assert(2 * 128 * kSoftmaxRegs + 128 * kHelperRegs <= kLaunchRegs * kThreads,
               "register hand-over does not balance");
-constexpr int kStagesK = 3, kStagesV = 3;
+constexpr int kStages = 3;       // K / V ring stages (the dense-tile bias form gives one of each to its bias tiles)
+constexpr int kStagesDense = 2;
 constexpr int kKLead = 2;                             // K tiles are consumed two iterations ahead of V tiles
 constexpr uint32_t kTmemCols = 512;                   // S0 S1 (128 each), O0 O1 (64 each), P0 P1 (64 each)
 constexpr uint32_t kTmemS = 0, kTmemO = 256, kTmemP = 384;
@@ -84,7 +86,10 @@ enum : int { kItemWhole = 0, kItemPartial = 1, kItemOwner = 2 };
 // tables of a row sit in registers and every column's pair of indices is a compile-time constant.
 // kBiasDecomposed64 is the decomposed form specialised for rel_kw == 64, rel_kh a multiple of 8, with 16-bit, 16-byte aligned
 // rel_w rows (SAM's global layers): a key tile then spans exactly two rel_h entries and the whole rel_w row twice.
-enum : int { kBiasNone = 0, kBiasDense = 1, kBiasDecomposed = 2, kBiasDecomposed64 = 3, kBiasDecomposed14 = 4 };
+// kBiasDenseTiles is the dense form for 16-bit biases whose rows are 16-byte aligned: the loader warp brings the
+// 128 x 128 bias tile of every (query tile, key tile) into shared memory with TMA, like K and V, instead of every
+// softmax thread walking its own row in global memory.
+enum : int { kBiasNone = 0, kBiasDense = 1, kBiasDecomposed = 2, kBiasDecomposed64 = 3, kBiasDecomposed14 = 4, kBiasDenseTiles = 5 };
 constexpr int kRelStageWords = 33;  // per-row staging of rel_h | rel_w in shared memory: up to 32 values, odd stride
 
 struct BiasView {
@@ -137,15 +142,19 @@ struct CtaWork {
   int steps_all, steps_pairs;  // key-tile steps of all items and of the two-tile items
 };
 
-struct alignas(1024) AttnSmem {
+template <int STAGES, bool BIAS_TILES>
+struct alignas(1024) AttnSmemT {
+  static constexpr int kRing = STAGES;
   uint8_t q[2][2][kTileBytes];  // [query-tile slot][item parity]: the next item's Q is loaded while this one computes
-  uint8_t k[kStagesK][kTileBytes];
-  uint8_t v[kStagesV][kTileBytes];
+  uint8_t k[STAGES][kTileBytes];
+  uint8_t v[STAGES][kTileBytes];
   uint8_t o_stage[2][kTileBytes];  // an item's output tile per query-tile slot, in the TMA tile layout (128-byte swizzle)
   uint64_t q_full[2][2];   // Q_t of an item has landed                      (TMA)
   uint64_t q_empty[2][2];  // that item's last Q_t K^T has finished          (MMA commit)
-  uint64_t k_full[kStagesK], k_empty[kStagesK];
-  uint64_t v_full[kStagesV], v_empty[kStagesV];
+  uint64_t k_full[STAGES], k_empty[STAGES];
+  uint64_t v_full[STAGES], v_empty[STAGES];
+  uint64_t bias_full[2];   // dense-tile bias form: the bias tile of query tile t's current step has landed (TMA)
+  uint64_t bias_free[2];   // ... and has been read by the softmax warps                                  (4 softmax warps)
   uint64_t s_full[2];   // S_t(j) is in tensor memory                     (MMA commit)
   uint64_t s_free[2];   // S_t(j) has been read into registers             (4 softmax warps)
   uint64_t p_full[2];   // P_t(j) is in tensor memory, O_t rescaled        (4 softmax warps)
@@ -161,8 +170,17 @@ struct alignas(1024) AttnSmem {
   uint32_t tmem_base;
   uint32_t abort;
   CtaWork work;  // written once at set-up; kept here rather than in registers of every role
-  float rel_stage[2][kTileRows][kRelStageWords];  // each softmax thread's own rel_h | rel_w row, times log2(e)
+  // decomposed forms: each softmax thread's own rel_h | rel_w row, times log2(e); dense-tile form: per query tile the
+  // two 64-column halves of the current 128 x 128 bias tile (16-bit, 128-byte swizzle)
+  // (a TMA destination with the 128-byte swizzle starts on a 1024-byte boundary)
+  union alignas(BIAS_TILES ? 1024 : 16) {
+    float rel_stage[2][kTileRows][kRelStageWords];
+    uint8_t bias_tile[BIAS_TILES ? 2 : 1][2][BIAS_TILES ? kTileBytes : 16];
+  };
 };
+using AttnSmem = AttnSmemT<kStages, false>;
+using AttnSmemDense = AttnSmemT<kStagesDense, true>;
+static_assert(offsetof(AttnSmemDense, bias_tile) % 1024 == 0, "bias tiles: 1024-byte aligned for the 128-byte swizzle");
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -303,7 +321,7 @@ __device__ __forceinline__ void add_rel14(float* s, const float* stage, float c)
   }
 }
 
-static_assert(sizeof(AttnSmem) + 1024 <= 227 * 1024, "shared memory of one CTA");
+static_assert(sizeof(AttnSmem) + 1024 <= 227 * 1024 && sizeof(AttnSmemDense) + 1024 <= 227 * 1024, "shared memory of one CTA");
 
 // One unit of work: one or two 128-row query tiles of one (batch, head) over the key tiles [ja, jb).
 struct WorkItem {
@@ -483,9 +501,12 @@ __device__ __forceinline__ void merge_parts_to_output(float* ws_partial, T* out_
 template <typename T, int BIAS, bool SHORT, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const AttnParams p) {
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                const __grid_constant__ CUtensorMap tm_bias, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
-  AttnSmem& sm = *reinterpret_cast<AttnSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using Smem = std::conditional_t<BIAS == kBiasDenseTiles, AttnSmemDense, AttnSmem>;
+  constexpr int kStagesK = Smem::kRing, kStagesV = Smem::kRing;
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -510,6 +531,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&sm.turn[i], 4);
       mbar_init(&sm.o_staged[i], 4);
       mbar_init(&sm.o_stage_free[i], 1);
+      mbar_init(&sm.bias_full[i], 1);
+      mbar_init(&sm.bias_free[i], 4);
       mbar_init(&sm.merge_go[i], 1);
       mbar_init(&sm.drain[i], 1);
     }
@@ -534,6 +557,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
     tma_prefetch_desc(&tm_o);
+    if constexpr (BIAS == kBiasDenseTiles) tma_prefetch_desc(&tm_bias);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -601,6 +625,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             mbar_wait_relaxed(&sm.k_full[j % kStagesK], (j / kStagesK) & 1, &no_abort);
           for (int j = (gv > kStagesV ? gv - kStagesV : 0); j < gv; ++j)
             mbar_wait_relaxed(&sm.v_full[j % kStagesV], (j / kStagesV) & 1, &no_abort);
+        }
+      }
+      if constexpr (BIAS == kBiasDenseTiles) {
+        // A second lane of the loader warp brings the bias tiles: one 128 x 128 tile (two 64-column boxes) per query
+        // tile and step, single-buffered per query tile. It runs at the softmax warps' pace (a tile's buffer is free
+        // once they have read the previous one, early in a step), which must not hold up the K / V loads that run
+        // tiles ahead: hence a lane of its own. Columns and rows past the end of the bias read as zero.
+        if (lane == 1) {
+          bool ok = true;
+          int gb[2] = {0, 0};  // bias tiles issued so far per query-tile slot
+          for (int it = 0; it < my_items && ok; ++it) {
+            const WorkItem w = decode_item<SPLIT>(p, cw, it);
+            for (int j = w.ja; j < w.jb && ok; ++j) {
+              for (int t = 0; t < w.n_tiles && ok; ++t) {
+                ok = mbar_wait_relaxed(&sm.bias_free[t], (gb[t] & 1) ^ 1, abort_flag);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&sm.bias_full[t], 2 * kTileBytes);
+                const int bz = p.bias.sh != 0 ? w.h : 0, bw = p.bias.sb != 0 ? w.b : 0;  // a stride of 0 broadcasts
+                tma_load_4d(sm.bias_tile[t][0], &tm_bias, &sm.bias_full[t], j * kTileRows, w.q_row0 + t * kTileRows, bz, bw);
+                tma_load_4d(sm.bias_tile[t][1], &tm_bias, &sm.bias_full[t], j * kTileRows + 64, w.q_row0 + t * kTileRows, bz, bw);
+                ++gb[t];
+              }
+            }
+          }
+          if (!ok) {
+            if (atomicExch(const_cast<uint32_t*>(abort_flag), 1u) == 0) atomicOr(p.status, kStatusLoader);
+          }
+          if (*abort_flag != 0) {  // let the copies in flight land (at most one tile per slot)
+            uint32_t no_abort = 0;
+            for (int t = 0; t < 2; ++t)
+              if (gb[t] > 0) mbar_wait_relaxed(&sm.bias_full[t], (gb[t] - 1) & 1, &no_abort);
+          }
         }
       }
       __syncwarp();
@@ -1064,7 +1120,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int kv_valid = min(kTileRows, p.kv_tokens - kv0);
         float rh0 = 0.f, rh1 = 0.f;  // kBiasDecomposed64: rel_h of the tile's two 64-column halves, natural units
 
-        if constexpr (BIAS == kBiasDense) {
+        if constexpr (BIAS == kBiasDenseTiles) {
+          // The tile is in shared memory (loader warp, TMA): this thread's row is sixteen 16-byte chunks, eight per
+          // 64-column half, at the positions of the 128-byte swizzle. Logits stay in natural units, s * scale + bias,
+          // one packed FMA per pair of columns; log2(e) rides on the FMA in front of the exponential.
+          bad |= !mbar_wait_warp(&sm.bias_full[t], step & 1, abort_flag);
+          const bool is_half = p.bias.dtype == 0;
+          const float scale_nat = c * 0.6931471805599453f;  // scale_log2 / log2(e)
+          auto add_tile = [&](auto half_tag) {
+            constexpr bool kHalf = decltype(half_tag)::value;
+            const float2 cc = make_float2(scale_nat, scale_nat);
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              const uint32_t row = smem_u32(sm.bias_tile[t][hf]) + row_in_tile * 128;
+#pragma unroll
+              for (int ch = 0; ch < 8; ++ch) {
+                const uint4 v = ld_shared_v4(row + ((ch ^ (row_in_tile & 7)) << 4));
+                const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int i = hf * 64 + ch * 8 + e * 2;
+                  const float2 r = ffma2(make_float2(s[i], s[i + 1]), cc, unpack2(w4[e], kHalf));
+                  s[i] = r.x;
+                  s[i + 1] = r.y;
+                }
+              }
+            }
+          };
+          if (is_half) add_tile(std::true_type{});
+          else add_tile(std::false_type{});
+          warp_arrive(&sm.bias_free[t], lane);  // the loader may bring the next step's tile
+        } else if constexpr (BIAS == kBiasDense) {
           if (p.bias_vec && kv_valid == kTileRows && p.bias.dtype != 2) {
             // 16-bit bias, aligned rows, full tile: 32 columns (four 16-byte loads) at a time
             const bool is_half = p.bias.dtype == 0;
@@ -1204,6 +1290,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           mx1 = max3(mx1, s[126], s[127]);
           m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
           if constexpr (BIAS == kBiasNone) m_tile *= c;
+          if constexpr (BIAS == kBiasDenseTiles) m_tile *= kLog2e;  // natural units -> base-2 units
         }
 
         // Raise the reference maximum only when it pays (or on the first tile).
@@ -1225,7 +1312,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (need_turn) bad |= !mbar_wait_warp_after(turn_early, &sm.turn[t], turn_parity, abort_flag);
         float2 l2a = make_float2(0.f, 0.f), l2b = make_float2(0.f, 0.f);
         const float2 c2 = (BIAS == kBiasNone)           ? make_float2(c, c)
-                          : (BIAS == kBiasDecomposed64) ? make_float2(kLog2e, kLog2e)
+                          : (BIAS == kBiasDecomposed64 || BIAS == kBiasDenseTiles) ? make_float2(kLog2e, kLog2e)
                                                         : make_float2(1.f, 1.f);
         float nm = -m_use;
         uint32_t pk[kTileRows / 2];

@@ -235,7 +235,7 @@ int validate(const B200AttnArgs* a, int* bias_mode, int* schedule) {
 // status word and which kernels already have their shared-memory opt-in (the opt-in is per device and per kernel).
 // The runtime calls behind these cost more than the rest of the host path of a launch-bound call.
 constexpr int kMaxDevices = 64;
-constexpr int kKernelForms = 30;  // 2 dtypes x 5 bias forms x (short, long, long with key split)
+constexpr int kKernelForms = 36;  // 2 dtypes x 6 bias forms x (short, long, long with key split)
 struct DeviceState {
   std::atomic<bool> ready{false};
   int sms = 0;
@@ -392,9 +392,9 @@ unsigned plan_work(AttnParams& prm, const B200AttnArgs* a, int sms) {
 
 template <typename T, int BIAS, bool SHORT, bool SPLIT>
 int launch(const AttnParams& planned, unsigned grid, DeviceState& dev, const CUtensorMap& mq, const CUtensorMap& mk,
-           const CUtensorMap& mv, const CUtensorMap& mo, cudaStream_t stream) {
+           const CUtensorMap& mv, const CUtensorMap& mo, const CUtensorMap& mb, cudaStream_t stream) {
   auto kernel = attn_fwd_kernel<T, BIAS, SHORT, SPLIT>;
-  constexpr int smem = static_cast<int>(sizeof(AttnSmem)) + 1024;
+  constexpr int smem = static_cast<int>(BIAS == kBiasDenseTiles ? sizeof(AttnSmemDense) : sizeof(AttnSmem)) + 1024;
   constexpr int form = (BIAS * 2 + (std::is_same<T, __half>::value ? 0 : 1)) * 3 + (SHORT ? 1 : SPLIT ? 2 : 0);
   static_assert(form < kKernelForms, "kernel form index");
   if (!dev.opted_in[form].load(std::memory_order_acquire)) {
@@ -417,7 +417,7 @@ int launch(const AttnParams& planned, unsigned grid, DeviceState& dev, const CUt
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
   config.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&config, kernel, mq, mk, mv, mo, planned);
+  cudaError_t e = cudaLaunchKernelEx(&config, kernel, mq, mk, mv, mo, mb, planned);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "attention kernel launch");
   return B200_ATTN_OK;
@@ -428,12 +428,69 @@ int launch(const AttnParams& planned, unsigned grid, DeviceState& dev, const CUt
 // sequence of at most two key tiles is never split).
 template <typename T, int BIAS>
 int launch_sched(bool short_sched, const AttnParams& planned, unsigned grid, DeviceState& dev, const CUtensorMap& mq,
-                 const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, cudaStream_t stream) {
-  if (planned.chunked) return launch<T, BIAS, false, true>(planned, grid, dev, mq, mk, mv, mo, stream);
+                 const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, const CUtensorMap& mb, cudaStream_t stream) {
+  if (planned.chunked) return launch<T, BIAS, false, true>(planned, grid, dev, mq, mk, mv, mo, mb, stream);
   if constexpr (BIAS != kBiasDecomposed64) {
-    if (short_sched) return launch<T, BIAS, true, false>(planned, grid, dev, mq, mk, mv, mo, stream);
+    if (short_sched) return launch<T, BIAS, true, false>(planned, grid, dev, mq, mk, mv, mo, mb, stream);
   }
-  return launch<T, BIAS, false, false>(planned, grid, dev, mq, mk, mv, mo, stream);
+  return launch<T, BIAS, false, false>(planned, grid, dev, mq, mk, mv, mo, mb, stream);
+}
+
+// The dense bias [B | 1, H | 1, Nq, Nk] (a stride of 0 broadcasts that dimension) as a 4-D tensor map whose box is
+// 128 rows x 64 columns with the 128-byte swizzle; a broadcast dimension gets extent 1 and the kernel addresses it at 0.
+int make_bias_map(CUtensorMap* map, const B200AttnArgs* a) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr) return fail(B200_ATTN_CUDA_ERROR_BASE, "cuTensorMapEncodeTiled is not available from this driver");
+  const int64_t sb = a->batch > 1 ? a->bias_stride[0] : 0, sh = a->heads > 1 ? a->bias_stride[1] : 0, sn = a->bias_stride[2];
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(a->kv_tokens), static_cast<cuuint64_t>(a->q_tokens),
+                        static_cast<cuuint64_t>(sh != 0 ? a->heads : 1), static_cast<cuuint64_t>(sb != 0 ? a->batch : 1)};
+  // a dimension of extent 1 is only ever addressed at 0: any legal stride will do
+  const int64_t row = a->q_tokens > 1 ? sn : a->kv_tokens + (8 - a->kv_tokens % 8) % 8;
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(row) * 2, static_cast<cuuint64_t>(dims[2] > 1 ? sh : row) * 2,
+                           static_cast<cuuint64_t>(dims[3] > 1 ? sb : row) * 2};
+  cuuint32_t box[4] = {64, kTileRows, 1, 1};
+  cuuint32_t elem[4] = {1, 1, 1, 1};
+  const CUresult r = enc(map, a->bias_dtype == B200_ATTN_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                         const_cast<void*>(a->bias), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(B200_ATTN_UNSUPPORTED, "tensor map for the bias rejected by the driver (CUresult %d)", static_cast<int>(r));
+  return B200_ATTN_OK;
+}
+
+// The bias maps a thread made last, like the tile maps of q, k, v and o: a model passes the same few bias tensors
+// call after call (one per block or per window shift).
+struct BiasMapKey {
+  const void* base;
+  int64_t stride[3];
+  int batch, heads, q_tokens, kv_tokens;
+  uint32_t dtype;
+  bool operator==(const BiasMapKey& o) const {
+    return base == o.base && stride[0] == o.stride[0] && stride[1] == o.stride[1] && stride[2] == o.stride[2] &&
+           batch == o.batch && heads == o.heads && q_tokens == o.q_tokens && kv_tokens == o.kv_tokens && dtype == o.dtype;
+  }
+};
+constexpr int kBiasMapSlots = 16;
+struct BiasMapCache {
+  BiasMapKey key[kBiasMapSlots];
+  CUtensorMap map[kBiasMapSlots];
+  bool used[kBiasMapSlots];
+};
+thread_local BiasMapCache tl_bias_maps{};
+
+int cached_bias_map(CUtensorMap* map, const B200AttnArgs* a) {
+  const BiasMapKey key{a->bias, {a->bias_stride[0], a->bias_stride[1], a->bias_stride[2]}, a->batch, a->heads,
+                       a->q_tokens, a->kv_tokens, a->bias_dtype};
+  const size_t slot = (reinterpret_cast<uintptr_t>(a->bias) >> 8) * 0x9E3779B97F4A7C15ull >> 60;  // 4 bits
+  BiasMapCache& c = tl_bias_maps;
+  if (c.used[slot] && c.key[slot] == key) {
+    *map = c.map[slot];
+    return B200_ATTN_OK;
+  }
+  if (const int rc = make_bias_map(map, a)) return rc;
+  c.key[slot] = key;
+  c.map[slot] = *map;
+  c.used[slot] = true;
+  return B200_ATTN_OK;
 }
 
 }  // namespace
@@ -479,6 +536,13 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
     // Vector loads need every row segment that starts at a multiple of 128 columns to be 16-byte aligned.
     prm.bias_vec = aligned16(a->bias) && a->bias_stride[0] % 8 == 0 && a->bias_stride[1] % 8 == 0 &&
                    a->bias_stride[2] % 8 == 0;
+    // 16-bit, 16-byte aligned rows: the bias comes in tiles through TMA like K and V
+    // (the stride of a dimension of extent 1 is never used)
+    const int64_t tb = a->batch > 1 ? a->bias_stride[0] : 0, th = a->heads > 1 ? a->bias_stride[1] : 0;
+    const int64_t tn = a->q_tokens > 1 ? a->bias_stride[2] : 8;
+    if (aligned16(a->bias) && a->bias_dtype != B200_ATTN_F32 && tn > 0 && tn % 8 == 0 && tb >= 0 && tb % 8 == 0 &&
+        th >= 0 && th % 8 == 0 && tn < (int64_t(1) << 38) && tb < (int64_t(1) << 38) && th < (int64_t(1) << 38))
+      bias_mode = kBiasDenseTiles;
   } else if (bias_mode == kBiasDecomposed) {
     prm.bias = BiasView{a->rel_h, a->rel_h_stride[0], a->rel_h_stride[1], a->rel_h_stride[2],
                         static_cast<int>(a->rel_dtype)};
@@ -502,25 +566,30 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
   if ((rc = device_state(&dev))) return rc;
   prm.status = dev->status;
 
+  CUtensorMap mb = mq;  // only the dense-tile bias form looks at it
+  if (bias_mode == kBiasDenseTiles && (rc = cached_bias_map(&mb, a))) return rc;
   const unsigned grid = plan_work(prm, a, dev->sms);
   const bool f16 = a->dtype == B200_ATTN_F16;
   const bool short_sched = sched == B200_ATTN_SCHED_SHORT;
   switch (bias_mode) {
     case kBiasNone:
-      return f16 ? launch_sched<__half, kBiasNone>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream)
-                 : launch_sched<__nv_bfloat16, kBiasNone>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream);
+      return f16 ? launch_sched<__half, kBiasNone>(short_sched, prm, grid, *dev, mq, mk, mv, mo, mb, stream)
+                 : launch_sched<__nv_bfloat16, kBiasNone>(short_sched, prm, grid, *dev, mq, mk, mv, mo, mb, stream);
+    case kBiasDenseTiles:
+      return f16 ? launch_sched<__half, kBiasDenseTiles>(short_sched, prm, grid, *dev, mq, mk, mv, mo, mb, stream)
+                 : launch_sched<__nv_bfloat16, kBiasDenseTiles>(short_sched, prm, grid, *dev, mq, mk, mv, mo, mb, stream);
     case kBiasDense:
-      return f16 ? launch_sched<__half, kBiasDense>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream)
-                 : launch_sched<__nv_bfloat16, kBiasDense>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream);
+      return f16 ? launch_sched<__half, kBiasDense>(short_sched, prm, grid, *dev, mq, mk, mv, mo, mb, stream)
+                 : launch_sched<__nv_bfloat16, kBiasDense>(short_sched, prm, grid, *dev, mq, mk, mv, mo, mb, stream);
     case kBiasDecomposed64:
-      return f16 ? launch_sched<__half, kBiasDecomposed64>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream)
-                 : launch_sched<__nv_bfloat16, kBiasDecomposed64>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream);
+      return f16 ? launch_sched<__half, kBiasDecomposed64>(short_sched, prm, grid, *dev, mq, mk, mv, mo, mb, stream)
+                 : launch_sched<__nv_bfloat16, kBiasDecomposed64>(short_sched, prm, grid, *dev, mq, mk, mv, mo, mb, stream);
     case kBiasDecomposed14:
-      return f16 ? launch_sched<__half, kBiasDecomposed14>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream)
-                 : launch_sched<__nv_bfloat16, kBiasDecomposed14>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream);
+      return f16 ? launch_sched<__half, kBiasDecomposed14>(short_sched, prm, grid, *dev, mq, mk, mv, mo, mb, stream)
+                 : launch_sched<__nv_bfloat16, kBiasDecomposed14>(short_sched, prm, grid, *dev, mq, mk, mv, mo, mb, stream);
     default:
-      return f16 ? launch_sched<__half, kBiasDecomposed>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream)
-                 : launch_sched<__nv_bfloat16, kBiasDecomposed>(short_sched, prm, grid, *dev, mq, mk, mv, mo, stream);
+      return f16 ? launch_sched<__half, kBiasDecomposed>(short_sched, prm, grid, *dev, mq, mk, mv, mo, mb, stream)
+                 : launch_sched<__nv_bfloat16, kBiasDecomposed>(short_sched, prm, grid, *dev, mq, mk, mv, mo, mb, stream);
   }
 }
 

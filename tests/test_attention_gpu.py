@@ -162,6 +162,71 @@ def test_dense_bias_broadcast_and_mask(bias_dtype: torch.dtype) -> None:
     assert_close(got.float().cpu().numpy(), ref, unit_scale=True)
 
 
+@pytest.mark.parametrize(
+    ("b", "h", "nq", "nk", "bias_shape", "pad"),
+    [
+        (3, 4, 144, 144, (1, 4, 144, 144), 0),  # short schedule, broadcast over the batch
+        (2, 3, 200, 200, (2, 1, 200, 200), 0),  # broadcast over the heads, ragged last tile
+        (2, 3, 150, 77, (2, 3, 150, 77), 3),  # cross lengths; rows padded to 80 columns in a wider buffer
+        (1, 2, 700, 1000, (1, 1, 700, 1000), 0),  # long schedule, one bias for everything
+        (2, 5, 1370, 1370, (1, 5, 1370, 1370), 6),  # 518-px token count, rows padded to 1376
+        (1, 2, 1, 64, (1, 2, 1, 64), 0),  # a single query row
+    ],
+)
+@pytest.mark.parametrize("bias_dtype", [torch.float16, torch.bfloat16])
+def test_dense_bias_in_tiles(b: int, h: int, nq: int, nk: int, bias_shape: tuple[int, ...], pad: int, bias_dtype: torch.dtype) -> None:
+    """A 16-bit bias whose rows start on 16-byte boundaries reaches the kernel as 128 x 64 tiles through TMA (the
+    other layouts take the row-wise loads): every broadcast form, padded rows, -inf columns, short and long schedule."""
+    gen = torch.Generator().manual_seed(nq * 7 + nk)
+    q = torch.randn(b, h, nq, 64, generator=gen).half().cuda()
+    k, v = (torch.randn(b, h, nk, 64, generator=gen).half().cuda() for _ in range(2))
+    bias = torch.randn(*bias_shape, generator=gen).to(bias_dtype)
+    bias[..., nk - nk // 5 :] = float("-inf")
+    bias[..., 0, :] = 3.0  # a row without any masked key
+    wide = torch.full((*bias_shape[:3], nk + pad), 9.0, dtype=bias_dtype).cuda()
+    wide[..., :nk] = bias.cuda()
+    dev_bias = wide[..., :nk]
+    assert (dev_bias.stride(2) % 8 == 0 or nq == 1) and dev_bias.data_ptr() % 16 == 0
+    got = ff.scaled_dot_product_attention(q, k, v, attn_mask=dev_bias)
+    assert ff.device_status() == 0
+    ref = ao.attention(*(t.float().cpu().numpy() for t in (q, k, v)), 0.125, bias.float().numpy())
+    assert_close(got.float().cpu().numpy(), ref, unit_scale=True, what=f"tiles {bias_shape} {bias_dtype}")
+    # the same numbers through the row-wise loads: float32 values, and the 16-bit rows at an odd stride taken as given
+    rowwise = ff.scaled_dot_product_attention(q, k, v, attn_mask=dev_bias.float())
+    assert_close(got.float().cpu().numpy(), rowwise.float().cpu().numpy(), unit_scale=True, what="tiles against float32 rows")
+    odd = torch.empty((*bias_shape[:3], nk + 1), dtype=bias_dtype).cuda()[..., :nk]
+    odd.copy_(dev_bias)
+    rowwise = ff.attention(q, k, v, bias=odd, _bias_as_given=True)
+    assert_close(got.float().cpu().numpy(), rowwise.float().cpu().numpy(), unit_scale=True, what="tiles against 16-bit rows")
+    # and `attention` pads such rows itself
+    padded = ff.attention(q, k, v, bias=odd)
+    assert torch.equal(padded, got)
+    assert ff.tile_layout(odd).stride(2) % 8 == 0 and torch.equal(ff.tile_layout(odd), odd)
+    assert ff.tile_layout(dev_bias).data_ptr() == dev_bias.data_ptr()
+
+
+def test_swin_window_bias_layout_of_the_reference() -> None:
+    """`_swin_bias` + `_swin_block` (src/fastforks/_optimize/transformer.py:455-479): windows folded into the head
+    dimension, one `[1, nw * heads, 49, 56]` table (relative-position bias plus the shift mask, rows padded to 8)
+    sliced to 49 columns and broadcast over the images."""
+    gen = torch.Generator().manual_seed(49)
+    images, nw, heads, n = 3, 16, 3, 49
+    q, k, v = (torch.randn(images, n, nw * heads, 64, generator=gen).half().cuda().transpose(1, 2) for _ in range(3))
+    table = torch.randn(1, nw * heads, n, n, generator=gen).half()
+    table[:, ::5, :7, 30:] = -100.0  # the shift mask of some windows
+    padded = torch.zeros(1, nw * heads, n, 56, dtype=torch.float16).cuda()
+    padded[..., :n] = table.cuda()
+    got = ff.scaled_dot_product_attention(q, k, v, attn_mask=padded[..., :n], scale=0.125)
+    ref = ao.attention(*(t.float().cpu().numpy() for t in (q, k, v)), 0.125, table.float().numpy())
+    assert_close(got.float().cpu().numpy(), ref, unit_scale=True, what="swin windows")
+    # the second call of a geometry is launched from its remembered description: new values, other memory
+    other = padded.clone()
+    other[..., :n] = 0.5 * table.cuda()
+    again = ff.scaled_dot_product_attention(q, k, v, attn_mask=other[..., :n], scale=0.125)
+    ref = ao.attention(*(t.float().cpu().numpy() for t in (q, k, v)), 0.125, 0.5 * table.float().numpy())
+    assert_close(again.float().cpu().numpy(), ref, unit_scale=True, what="swin windows, remembered launch")
+
+
 def test_bool_mask_like_sdpa() -> None:
     gen = torch.Generator().manual_seed(6)
     q, k, v = (torch.randn(1, 2, 70, 64, generator=gen).half().cuda() for _ in range(3))
