@@ -79,7 +79,12 @@ typedef struct B200AttnArgs {
 
   /* Optional dense additive bias (an SDPA `attn_mask` of floating type), added to scale * q k^T.
    * Element (b, h, i, j) at bias + b*bias_stride[0] + h*bias_stride[1] + i*bias_stride[2] + j.
-   * A stride of 0 broadcasts that dimension.  NULL = none. */
+   * A stride of 0 broadcasts that dimension.  NULL = none.
+   * A 16-bit bias whose base is 16-byte aligned and whose strides (of the dimensions with more than one entry) are
+   * multiples of 8 elements is fetched tile by tile through the tensor memory accelerator, like K and V; this is the
+   * layout the reference builds for its windowed blocks (rows padded to a multiple of 8 and sliced,
+   * src/fastforks/_optimize/transformer.py:463-466).  Any other layout, and fp32, is read row by row: same results,
+   * several times slower. */
   const void* bias;
   uint32_t bias_dtype; /* B200_ATTN_F16 / BF16 / F32 */
   int64_t bias_stride[3];
