@@ -1099,12 +1099,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         float s[kTileRows];
         {
           uint32_t* su = reinterpret_cast<uint32_t*>(s);
-          // Four loads in flight, one wait.
-#pragma unroll
-          for (int q = 0; q < 4; ++q) tmem_ld_x32_nowait(s_addr + 32 * q, su + 32 * q);
-          tmem_ld_wait_pin(su);
-#pragma unroll
-          for (int q = 1; q < 4; ++q) tmem_ld_pin(su + 32 * q);
+          // One 128-column load (a quarter of the tcgen05 instructions of four 32-column ones: -2 %).
+          tmem_ld_x128(s_addr, su);
         }
         // S_t is in registers: the tensor pipe may overwrite it with the tile after next.
         tc_fence_before_sync();
@@ -1306,9 +1302,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // ---- exponentials ---------------------------------------------------------------------------
         // Both warpgroups feed the MUFU unit, but they must not run in lockstep (their loads and reductions
         // would leave the unit idle together, and equal loops sharing a unit drift into lockstep). So each
-        // may only start a section once the other is half way through its previous one: warpgroup 0 starts
-        // step q+1 after warpgroup 1's midpoint of step q, warpgroup 1 starts step q after warpgroup 0's
-        // midpoint of step q. Half a section apart, neither ever waits here.
+        // may only start a section once the other has released it from inside its previous one: warpgroup 0
+        // starts step q+1 after warpgroup 1's release in step q, warpgroup 1 starts step q after warpgroup 0's
+        // release in step q. The release comes after 96 of the 128 columns in the long schedule (measured against
+        // 32, 64, 80, 112 and 128: 64 was 3 % slower on eleven key tiles, 128 - exclusive sections - 7 %) and
+        // after 64 in the short one.
         if (need_turn) bad |= !mbar_wait_warp_after(turn_early, &sm.turn[t], turn_parity, abort_flag);
         float2 l2a = make_float2(0.f, 0.f), l2b = make_float2(0.f, 0.f);
         const float2 c2 = (BIAS == kBiasNone)           ? make_float2(c, c)
@@ -1316,8 +1314,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                                         : make_float2(1.f, 1.f);
         float nm = -m_use;
         uint32_t pk[kTileRows / 2];
-        // Midpoint of the section: let the other warpgroup start (the rest of the section reads `nm` through the
-        // arrival, which pins it in the instruction stream) and issue the tests of the barriers needed next.
+        // Release point of the section: let the other warpgroup start (the rest of the section reads `nm` through
+        // the arrival, which pins it in the instruction stream) and issue the tests of the barriers needed next.
         auto midpoint = [&]() {
           if (pingpong) warp_arrive_pinned(&sm.turn[t ^ 1], lane, nm);
           // On an item's first tile the P V in question is the last one of the pending item (same barrier, and
@@ -1346,8 +1344,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         };
         using std::integral_constant;
         exp_columns(integral_constant<int, 0>{}, integral_constant<int, 2>{});
-        midpoint();
         if constexpr (SHORT) {
+          midpoint();
           // Short-sequence schedule. The last 32 columns of a ragged last key tile that hold no key at all (197 keys:
           // 69 in the second tile) need no exponentials: their logits are -inf and their P is never read (P V stops
           // at the last key's k-step). One CTA-uniform branch: -6 % on [256,12,197,64]. With eleven key tiles
@@ -1361,7 +1359,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int i = 48; i < 64; ++i) pk[i] = 0u;
           }
         } else {
-          exp_columns(integral_constant<int, 2>{}, integral_constant<int, 2>{});
+          exp_columns(integral_constant<int, 2>{}, integral_constant<int, 1>{});
+          midpoint();
+          exp_columns(integral_constant<int, 3>{}, integral_constant<int, 1>{});
         }
         l_sum += (l2a.x + l2a.y) + (l2b.x + l2b.y);
 
@@ -1387,8 +1387,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tmem_st_x32(o_addr + 32, ou + 32);
           }
         }
-        tmem_st_x32(p_addr, pk);
-        tmem_st_x32(p_addr + 32, pk + 32);
+        tmem_st_x64(p_addr, pk);
         tmem_st_wait();
         tc_fence_before_sync();
         warp_arrive(&sm.p_full[t], lane);
