@@ -69,6 +69,7 @@ AUX_CASES = {
     "gemm-4k": "gemm [4096,4096] x [4096,4096]^T bf16, no epilogue terms",
     "sam-rel-global": "sam_rel_terms of q [1,4096,12,64] fp16, 64 x 64 grid",
     "sam-rel-windows": "sam_rel_terms of q [25,196,12,64] fp16, 14 x 14 grid",
+    "rope-dinov3-vitl": "rope_qk_ of qkv [32,1029,3,16,64] fp16 in place (DINOv3 ViT-L/16 at 512 px): 270 MB read + written, time per launch reported",
 }
 # DRAM bytes of one launch of the headline kernel ([8,6,1370,64] fp16): dram__bytes_read.sum + dram__bytes_write.sum
 # of one profiler capture of `python bench.py --case dinov2-vits14` (q, k, v are read once, 25.3 MB; the 8.4 MB output
@@ -575,6 +576,22 @@ def run_case(args: argparse.Namespace) -> None:
                     ff.gemm(x, w, bias)
                 else:
                     ff.gemm(x, w)
+        elif args.case.startswith("rope"):
+            qkv = rnd(32, 5 + 32 * 32, 3, 16, HEAD_DIM, dt=torch.float16)
+            cs = ff.rope_table(32, 32, 100.0, "cuda")
+            ff.rope_qk_(qkv, cs, q_scale=0.125)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.launches):
+                ff.rope_qk_(qkv, cs, q_scale=0.125)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / args.launches * 1e3
+            moved = 2 * 2 * qkv.shape[0] * qkv.shape[1] * 16 * HEAD_DIM * 2  # q and k, read and written
+            print(json.dumps({"case": args.case, "what": AUX_CASES[args.case], "launches": args.launches, "us_per_launch": us,
+                              "gbs": moved / us / 1e3, "status": ff.device_status()}))  # fmt: skip
+            return
         else:
             b, side = (1, 64) if args.case == "sam-rel-global" else (25, 14)
             q = rnd(b, side * side, 3, 12, HEAD_DIM, dt=torch.float16)[:, :, 0]

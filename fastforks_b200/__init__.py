@@ -18,6 +18,7 @@ from .errors import BackendUnavailableError, KernelUnavailableError
 from .gemm import ACT_GELU, ACT_GELU_TANH, ACT_NONE, ACT_RELU, gemm
 from .flash64 import FLASH_VARIANTS, Flash64, check_flash64
 from .host_io import HostAttention
+from .rope import rope_qk_, rope_table
 from .sam import sam_rel_terms
 from .sdpa import scaled_dot_product_attention
 
@@ -40,6 +41,8 @@ __all__ = [
     "kernels_unavailable_reason",
     "reserve_workspace",
     "resolve_mode",
+    "rope_qk_",
+    "rope_table",
     "sam_rel_terms",
     "tile_layout",
     "scaled_dot_product_attention",

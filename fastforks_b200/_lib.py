@@ -26,6 +26,7 @@ HEADERS = (
     PACKAGE_DIR / "csrc" / "sm100_ptx.cuh",
     PACKAGE_DIR / "csrc" / "attn_fwd_sm100.cuh",
     PACKAGE_DIR / "csrc" / "sam_rel_terms.cuh",
+    PACKAGE_DIR / "csrc" / "rope_sm100.cuh",
     PACKAGE_DIR / "csrc" / "gemm_sm100.cuh",
     PACKAGE_DIR.parent / "include" / "b200_attn.h",
 )
@@ -39,7 +40,7 @@ NVCC_FLAGS = (
 
 # Every symbol include/b200_attn.h declares.
 EXPORTS = (
-    "b200_attn_fwd", "b200_attn_fwd_static", "b200_gemm", "b200_sam_rel_terms", "b200_attn_query", "b200_attn_plan", "b200_attn_workspace_size", "b200_attn_status",
+    "b200_attn_fwd", "b200_attn_fwd_static", "b200_gemm", "b200_sam_rel_terms", "b200_rope_qk", "b200_attn_query", "b200_attn_plan", "b200_attn_workspace_size", "b200_attn_status",
     "b200_attn_selftest_wait_limit", "b200_attn_last_error", "b200_attn_version",
 )  # fmt: skip
 
@@ -126,6 +127,26 @@ class B200RelTermsArgs(ctypes.Structure):
     )
 
 
+class B200RopeArgs(ctypes.Structure):
+    """Mirror of `struct B200RopeArgs` (include/b200_attn.h)."""
+
+    _fields_ = (
+        ("struct_size", ctypes.c_uint32),
+        ("dtype", ctypes.c_uint32),
+        ("q", ctypes.c_void_p),
+        ("k", ctypes.c_void_p),
+        ("q_stride", ctypes.c_int64 * 3),
+        ("k_stride", ctypes.c_int64 * 3),
+        ("cs", ctypes.c_void_p),
+        ("batch", ctypes.c_int32),
+        ("heads", ctypes.c_int32),
+        ("tokens", ctypes.c_int32),
+        ("prefix", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32),
+        ("q_scale", ctypes.c_float),
+    )
+
+
 def source_hash() -> str:
     """Digest of the sources the shared object is compiled from (16 hex digits). The build passes it to the compiler,
     which puts it into the library's version string, so a binary can be matched with the sources beside it."""
@@ -206,6 +227,8 @@ def library() -> ctypes.CDLL:
     lib.b200_gemm.restype = ctypes.c_int
     lib.b200_sam_rel_terms.argtypes = (ctypes.POINTER(B200RelTermsArgs), ctypes.c_void_p)
     lib.b200_sam_rel_terms.restype = ctypes.c_int
+    lib.b200_rope_qk.argtypes = (ctypes.POINTER(B200RopeArgs), ctypes.c_void_p)
+    lib.b200_rope_qk.restype = ctypes.c_int
     lib.b200_attn_query.argtypes = (ctypes.POINTER(B200AttnArgs), ctypes.POINTER(ctypes.c_int32))
     lib.b200_attn_query.restype = ctypes.c_int
     i32p = ctypes.POINTER(ctypes.c_int32)

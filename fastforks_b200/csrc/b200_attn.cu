@@ -17,6 +17,7 @@
 
 #include "attn_fwd_sm100.cuh"
 #include "gemm_sm100.cuh"
+#include "rope_sm100.cuh"
 #include "sam_rel_terms.cuh"
 
 namespace {
@@ -819,6 +820,52 @@ int b200_sam_rel_terms(const B200RelTermsArgs* a, void* stream_ptr) {
   else sam_rel_terms_kernel<__nv_bfloat16><<<grid, kRelThreads, 0, stream>>>(prm);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "sam_rel_terms kernel launch");
+  tl_error[0] = '\0';
+  return B200_ATTN_OK;
+}
+
+int b200_rope_qk(const B200RopeArgs* a, void* stream_ptr) {
+  if (a == nullptr) return fail(B200_ATTN_BAD_CONFIG, "args is NULL");
+  if (a->struct_size != sizeof(B200RopeArgs))
+    return fail(B200_ATTN_BAD_CONFIG, "struct_size %u does not match this library's B200RopeArgs (%zu bytes)",
+                a->struct_size, sizeof(B200RopeArgs));
+  if (a->dtype != B200_ATTN_F16 && a->dtype != B200_ATTN_BF16)
+    return fail(B200_ATTN_BAD_CONFIG, "dtype %u: q and k must be fp16 (0) or bf16 (1)", a->dtype);
+  if (a->head_dim != kHeadDim) return fail(B200_ATTN_UNSUPPORTED, "head_dim %d: only head dim 64 is built", a->head_dim);
+  if (a->batch < 1 || a->heads < 1 || a->tokens < 1 || a->prefix < 0 || a->prefix > a->tokens)
+    return fail(B200_ATTN_BAD_CONFIG, "batch %d heads %d tokens %d prefix %d", a->batch, a->heads, a->tokens, a->prefix);
+  if (!(a->q_scale > 0.f) || !std::isfinite(a->q_scale)) return fail(B200_ATTN_BAD_CONFIG, "q_scale must be positive and finite");
+  if (int rc = check_view("q", a->q, a->q_stride, a->batch, a->heads, a->tokens)) return rc;
+  if (int rc = check_view("k", a->k, a->k_stride, a->batch, a->heads, a->tokens)) return rc;
+  if (a->prefix < a->tokens) {
+    if (a->cs == nullptr) return fail(B200_ATTN_BAD_CONFIG, "cs is NULL");
+    if (!aligned16(a->cs)) return fail(B200_ATTN_UNSUPPORTED, "cs is not 16-byte aligned");
+  }
+  DeviceState* dev = nullptr;
+  if (int rc = device_state(&dev)) return rc;
+  RopeParams prm{};
+  prm.q = a->q;
+  prm.k = a->k;
+  prm.q_sb = a->q_stride[0];
+  prm.q_sn = a->q_stride[1];
+  prm.q_sh = a->q_stride[2];
+  prm.k_sb = a->k_stride[0];
+  prm.k_sn = a->k_stride[1];
+  prm.k_sh = a->k_stride[2];
+  prm.cs = a->cs;
+  prm.batch = a->batch;
+  prm.heads = a->heads;
+  prm.tokens = a->tokens;
+  prm.prefix = a->prefix;
+  prm.q_scale = a->q_scale;
+  // One token per CTA and pass; enough CTAs to fill every SM sixteen times over (128 threads each), no more.
+  const long long rows = static_cast<long long>(a->batch) * a->tokens;
+  const unsigned grid = static_cast<unsigned>(std::min<long long>(rows, static_cast<long long>(dev->sms) * 16));
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  if (a->dtype == B200_ATTN_F16) rope_qk_kernel<__half><<<grid, kRopeThreads, 0, stream>>>(prm);
+  else rope_qk_kernel<__nv_bfloat16><<<grid, kRopeThreads, 0, stream>>>(prm);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "rope_qk kernel launch");
   tl_error[0] = '\0';
   return B200_ATTN_OK;
 }

@@ -227,6 +227,36 @@ typedef struct B200RelTermsArgs {
 int b200_sam_rel_terms(const B200RelTermsArgs* args, void* stream);
 
 /*
+ * DINOv3's rotary position embedding, in place on q and k (head dim 64) before the attention call:
+ *     out[j]      = (x[j] cos[j] - x[j + 32] sin[j]) * m
+ *     out[j + 32] = (x[j + 32] cos[j] + x[j] sin[j]) * m        j = 0 .. 31,  m = q_scale for q, 1 for k
+ * computed in fp32 and rounded once.  It replaces the reference's `rope_qk_h` kernel
+ * (src/fastforks/kernels/fastbb/fastbb_kernels.cu:793-818; launched from src/fastforks/features/models/dinov3/model.py:199-201
+ * with q_scale = 64 ** -0.5, after which attention is called with scale 1.0).  q and k are views of the packed qkv
+ * tensor (element (b, n, head, d) at ptr + b*stride[0] + n*stride[1] + head*stride[2] + d, strides in elements,
+ * multiples of 8, base 16-byte aligned); `cs` is the reference's table, fp32 `[tokens - prefix, 2, 32]` = cos | sin of
+ * the patch tokens (model.py:185-188); the first `prefix` tokens of each sequence (class token and registers) are not
+ * rotated: their q is scaled, their k is left as it is.  Unlike the reference's kernel, bf16 is accepted too.
+ */
+typedef struct B200RopeArgs {
+  uint32_t struct_size; /* sizeof(B200RopeArgs) */
+  uint32_t dtype;       /* B200_ATTN_F16 or B200_ATTN_BF16 */
+  void* q;
+  void* k;
+  int64_t q_stride[3]; /* batch, token, head */
+  int64_t k_stride[3];
+  const float* cs;
+  int32_t batch;
+  int32_t heads;
+  int32_t tokens;
+  int32_t prefix;   /* 0 .. tokens */
+  int32_t head_dim; /* must be 64 */
+  float q_scale;
+} B200RopeArgs;
+
+int b200_rope_qk(const B200RopeArgs* args, void* stream);
+
+/*
  * Describes, without launching and without a GPU, the work the kernel's CTA number `cta` would do for `args` on a
  * device with `sms` SMs (148 on a B200): the grid size in *grid, the CTA's item count in *n_items, up to `max_items`
  * items as 7 integers each in `items` - batch, head, first query row, query tiles (1 or 2), first key tile, end key

@@ -248,6 +248,47 @@ def gemm_epilogue_case(seed: int) -> dict[str, np.ndarray]:
             "no_bias_residual": res + F.linear(x, w)}  # fmt: skip
 
 
+def dinov3_attention_case(seed: int, hw: tuple[int, int], dim: int, heads: int, std: float) -> dict[str, np.ndarray]:
+    """The reference's portable DINOv3 attention (`DINOv3ViT.attention`, features/models/dinov3/net.py:191-210) on one
+    seeded layer: q, k, v before RoPE, the rotated q and k it hands to SDPA, the input of the output projection, and
+    the half tables of `rope_table` in the layout of the kernels mode (model.py:185-188). 1 + 4 prefix tokens."""
+    import torch.nn.functional as F  # noqa: N812
+
+    from fastforks.features.models.dinov3 import net as dv3
+
+    gen = torch.Generator().manual_seed(seed)
+    cfg = dv3.Config(dim, heads, 1, 2 * dim, gated=False)
+    model = dv3.DINOv3ViT(cfg)
+    _init(model, gen, std)
+    blk = model.layer[0]
+    n = 1 + dv3.REGISTERS + hw[0] * hw[1]
+    y = torch.randn(2, n, dim, generator=gen)
+    rope = model.rope(hw[0], hw[1], torch.float32, y.device)
+    a = blk.attention
+    got: dict[str, torch.Tensor] = {}
+    qkv = torch.stack([p(y).view(2, n, heads, dim // heads).transpose(1, 2) for p in (a.q_proj, a.k_proj, a.v_proj)])
+    real_sdpa = F.scaled_dot_product_attention
+
+    def spy(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, **kw: object) -> torch.Tensor:
+        got.update(q_rot=q.detach().clone(), k_rot=k.detach().clone())
+        return real_sdpa(q, k, v, **kw)
+
+    h = a.o_proj.register_forward_pre_hook(lambda _m, i: got.__setitem__("out", i[0].detach().clone()))
+    dv3.F.scaled_dot_product_attention = spy
+    try:
+        with torch.no_grad():
+            model.attention(blk, y, rope)
+    finally:
+        dv3.F.scaled_dot_product_attention = real_sdpa
+        h.remove()
+    cos, sin = dv3.rope_table(hw[0], hw[1], dim // heads, cfg.rope_theta, y.device)
+    half = dim // heads // 2
+    return {"q": qkv[0].detach(), "k": qkv[1].detach(), "v": qkv[2].detach(), "q_rot": got["q_rot"], "k_rot": got["k_rot"],
+            "out": got["out"].view(2, n, heads, dim // heads).transpose(1, 2),
+            "cs": torch.stack((cos[:, :half], sin[:, :half]), 1), "hw": np.array(hw), "theta": np.float32(cfg.rope_theta),
+            "scale": np.float32((dim // heads) ** -0.5)}  # fmt: skip
+
+
 CASES = {
     # name: (builder, kwargs). Token counts follow the reference: 97 = its feature-golden input (112x168, patch 14),
     # 197 = ViT-B/16 at 224, 196 = one 14x14 SAM window; 8x16 exercises kh != kw.
@@ -267,6 +308,8 @@ CASES = {
     "model_timm_vitb16_blocks": (timm_blocks_case, {"seed": 12, "qk_gain": 4.0}),
     "model_sam_vitb_1024": (sam_encoder_case, {"seed": 13, "every": 2}),
     "gemm_epilogue": (gemm_epilogue_case, {"seed": 14}),
+    # DINOv3: rotary embedding on q and k in front of SDPA; 5 prefix tokens + a 6 x 5 patch grid
+    "dinov3_attention_6x5": (dinov3_attention_case, {"seed": 15, "hw": (6, 5), "dim": 128, "heads": 2, "std": 0.08}),
 }
 
 

@@ -29,7 +29,7 @@ def lib() -> ctypes.CDLL:
 
 def declared_functions() -> list[str]:
     text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
-    return re.findall(r"^\s*(?:const\s+)?[\w\*]+\s+\*?\s*(b200_(?:attn|sam|gemm)\w*)\s*\(", text, flags=re.M)
+    return re.findall(r"^\s*(?:const\s+)?[\w\*]+\s+\*?\s*(b200_(?:attn|sam|gemm|rope)\w*)\s*\(", text, flags=re.M)
 
 
 def test_header_declares_the_expected_entry_points() -> None:

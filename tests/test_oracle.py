@@ -89,3 +89,26 @@ def test_gemm_oracle_matches_the_torch_calls_of_the_portable_blocks() -> None:
     }
     for name, got in cases.items():
         np.testing.assert_allclose(got, g[name], rtol=0, atol=3e-5, err_msg=name)
+
+
+def test_rope_oracle_matches_the_reference_portable_dinov3_attention() -> None:
+    """`oracle/rope_oracle.py` against `tests/golden/dinov3_attention_6x5.npz` (the reference's `DINOv3ViT.attention` on
+    a seeded layer): the half tables of `rope_table`, and q and k as they reach SDPA, in the kernel's form
+    (`rope_qk`) and in the portable form (`rope_portable`); then the attention output from the rotated operands."""
+    from conftest import load_golden
+    from oracle import attention_oracle as ao
+    from oracle import rope_oracle as ro
+
+    g = load_golden("dinov3_attention_6x5")
+    h, w = (int(x) for x in g["hw"])
+    np.testing.assert_allclose(ro.rope_table(h, w, float(g["theta"])), g["cs"], rtol=0, atol=2e-6)
+    to_bnhd = lambda a: a.transpose(0, 2, 1, 3)  # noqa: E731 - golden tensors are [B, heads, N, d]
+    q_rot, k_rot = ro.rope_qk(to_bnhd(g["q"]), to_bnhd(g["k"]), g["cs"])
+    np.testing.assert_allclose(to_bnhd(q_rot), g["q_rot"], rtol=0, atol=5e-6)
+    np.testing.assert_allclose(to_bnhd(k_rot), g["k_rot"], rtol=0, atol=5e-6)
+    np.testing.assert_allclose(ro.rope_portable(g["q"], g["cs"]), g["q_rot"], rtol=0, atol=5e-6)
+    # the softmax scale on q commutes with the rotation and is exact for 2^-3
+    q_scaled, _ = ro.rope_qk(to_bnhd(g["q"]), to_bnhd(g["k"]), g["cs"], q_scale=0.125)
+    np.testing.assert_array_equal(q_scaled, q_rot * np.float32(0.125))
+    out = ao.attention(g["q_rot"], g["k_rot"], g["v"], float(g["scale"]))
+    np.testing.assert_allclose(out, g["out"], rtol=0, atol=5e-5)
