@@ -180,6 +180,11 @@ struct alignas(1024) AttnSmemT {
 };
 using AttnSmem = AttnSmemT<kStages, false>;
 using AttnSmemDense = AttnSmemT<kStagesDense, true>;
+// The set-up walks the barriers as one array and picks the arrival count by position.
+static_assert(offsetof(AttnSmem, merge_go) + sizeof(uint64_t[2]) == offsetof(AttnSmem, merge_ready) &&
+                  offsetof(AttnSmem, o_free) + 2 * sizeof(uint64_t[2]) == offsetof(AttnSmem, o_staged) &&
+                  offsetof(AttnSmem, q_full) < offsetof(AttnSmem, merge_go),
+              "barrier order in AttnSmemT: q_full ... o_free, turn, o_staged ... merge_go, nothing else in between");
 static_assert(offsetof(AttnSmemDense, bias_tile) % 1024 == 0, "bias tiles: 1024-byte aligned for the 128-byte swizzle");
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -517,36 +522,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int kv_last16 = (kv_last + 15) & ~15;
 
   // ---- set-up: barriers, tensor memory -------------------------------------------------------
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
-      for (int k = 0; k < 2; ++k) {
-        mbar_init(&sm.q_full[i][k], 1);
-        mbar_init(&sm.q_empty[i][k], 1);
-      }
-      mbar_init(&sm.s_full[i], 1);
-      mbar_init(&sm.s_free[i], 4);  // one arrival per softmax warp: 128 arrivals on one word take hundreds of clocks
-      mbar_init(&sm.p_full[i], 4);
-      mbar_init(&sm.pv_done[i], 1);
-      mbar_init(&sm.o_free[i], 4);
-      mbar_init(&sm.turn[i], 4);
-      mbar_init(&sm.o_staged[i], 4);
-      mbar_init(&sm.o_stage_free[i], 1);
-      mbar_init(&sm.bias_full[i], 1);
-      mbar_init(&sm.bias_free[i], 4);
-      mbar_init(&sm.merge_go[i], 1);
-      mbar_init(&sm.drain[i], 1);
+  // The barriers lie one after another in Smem (q_full first, merge_go last): the lanes of warp 0 share them out,
+  // one thread doing all fifty in turn was a visible part of a short launch. Arrival counts: 1 for a TMA
+  // transaction or an MMA commit, 4 for the warps of a softmax warpgroup (128 arrivals on one word take hundreds
+  // of clocks), 2 for the K / V rings' empty barriers (one commit per query tile; an item with one tile commits twice).
+  if (warp == 0) {
+    uint64_t* const first = &sm.q_full[0][0];
+    const int n_bars = static_cast<int>(&sm.merge_go[1] - first) + 1;
+    for (int i = lane; i < n_bars; i += 32) {
+      uint64_t* bar = first + i;
+      const bool four = (bar >= &sm.bias_free[0] && bar <= &sm.bias_free[1]) || (bar >= &sm.s_free[0] && bar <= &sm.s_free[1]) ||
+                        (bar >= &sm.p_full[0] && bar <= &sm.p_full[1]) || (bar >= &sm.o_free[0] && bar <= &sm.o_staged[1]);
+      const bool two = (bar >= &sm.k_empty[0] && bar <= &sm.k_empty[kStagesK - 1]) ||
+                       (bar >= &sm.v_empty[0] && bar <= &sm.v_empty[kStagesV - 1]);
+      mbar_init(bar, four ? 4 : two ? 2 : 1);
     }
-    for (int i = 0; i < kStagesK; ++i) {
-      mbar_init(&sm.k_full[i], 1);
-      mbar_init(&sm.k_empty[i], 2);  // one commit per query tile (an item with one tile commits twice)
-    }
-    for (int i = 0; i < kStagesV; ++i) {
-      mbar_init(&sm.v_full[i], 1);
-      mbar_init(&sm.v_empty[i], 2);
-    }
-    sm.abort = 0;
-    sm.work = cta_work(p, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
+    if (lane == 0) sm.abort = 0;
     mbar_init_fence();
+  } else if (threadIdx.x == 32) {
+    sm.work = cta_work(p, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
   }
   if (warp == kMmaWarp) {
     tmem_alloc(&sm.tmem_base, kTmemCols);
