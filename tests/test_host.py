@@ -103,6 +103,45 @@ def test_bias_view_broadcasts_without_copy() -> None:
         attn_mod._bias_view("bias", torch.zeros(5, 7, dtype=torch.int32), (2, 3, 5, 7), q)  # noqa: SLF001
 
 
+def test_tile_layout_pads_rows_only_where_needed() -> None:
+    """The layout the kernel fetches in tiles: 16-bit, 16-byte aligned base, strides of the dimensions with more than
+    one entry in multiples of 8. The reference builds its windowed blocks' bias that way itself (rows padded to a
+    multiple of 8 and sliced, src/fastforks/_optimize/transformer.py:463-466)."""
+    swin = torch.zeros(1, 12, 49, 56, dtype=torch.float16)[..., :49]  # the reference's `_swin_bias` layout
+    assert ff.tile_layout(swin).data_ptr() == swin.data_ptr()  # taken as it is
+    odd = torch.arange(2 * 3 * 5 * 7, dtype=torch.float32).reshape(2, 3, 5, 7).to(torch.bfloat16)
+    padded = ff.tile_layout(odd)
+    assert padded.shape == odd.shape and torch.equal(padded, odd)
+    assert padded.stride() == (3 * 5 * 8, 5 * 8, 8, 1) and padded.data_ptr() % 16 == 0
+    assert ff.tile_layout(padded).data_ptr() == padded.data_ptr()  # idempotent
+    # fewer dims are taken as broadcast over batch and heads; the stride of a dimension of one entry does not matter
+    two_d = ff.tile_layout(torch.zeros(5, 7, dtype=torch.float16))
+    assert two_d.shape == (1, 1, 5, 7) and two_d.stride(2) == 8
+    single_row = torch.zeros(1, 1, 1, 7, dtype=torch.float16)
+    assert ff.tile_layout(single_row).data_ptr() == single_row.data_ptr()
+    with pytest.raises(ValueError, match="float16 / bfloat16"):
+        ff.tile_layout(torch.zeros(5, 7))
+    # `attention` pads a 16-bit bias itself and reports the copy; a float32 bias is passed through for the row-wise loads
+    q = torch.zeros(2, 3, 5, 64, dtype=torch.float16)
+    view, copied = attn_mod._bias_view("bias", odd.half(), (2, 3, 5, 7), q, tiled=True)  # noqa: SLF001
+    assert copied and view.stride(2) == 8
+    view, copied = attn_mod._bias_view("bias", odd.float(), (2, 3, 5, 7), q, tiled=True)  # noqa: SLF001
+    assert not copied and view.stride(2) == 7
+
+
+def test_rope_table_and_contract_on_the_host() -> None:
+    """`rope_table` is plain torch and runs anywhere; `rope_qk_` rejects what the kernel cannot take before any launch."""
+    import numpy as np
+
+    from oracle import rope_oracle as ro
+
+    cs = ff.rope_table(3, 4, 100.0)
+    assert cs.shape == (12, 2, 32) and cs.dtype == torch.float32
+    np.testing.assert_allclose(cs.numpy(), ro.rope_table(3, 4, 100.0), rtol=0, atol=2e-6)
+    with pytest.raises(ValueError, match="CUDA"):
+        ff.rope_qk_(torch.zeros(1, 17, 3, 2, 64, dtype=torch.float16), cs)
+
+
 def test_resolve_mode_follows_the_reference_rule(caplog: pytest.LogCaptureFixture) -> None:
     assert ff.resolve_mode("portable") == "portable"
     with pytest.raises(ValueError, match="mode"):
