@@ -69,6 +69,8 @@ AUX_CASES = {
     "gemm-4k": "gemm [4096,4096] x [4096,4096]^T bf16, no epilogue terms",
     "sam-rel-global": "sam_rel_terms of q [1,4096,12,64] fp16, 64 x 64 grid",
     "sam-rel-windows": "sam_rel_terms of q [25,196,12,64] fp16, 14 x 14 grid",
+    "bias-swin": "attention [8,192,49,64] fp16 (Swin windows folded into the heads) + dense bias [1,192,49,56][..., :49] in tiles",
+    "bias-1370": "attention [8,16,1370,64] fp16 + dense bias [1,16,1370,1376][..., :1370] in tiles",
     "rope-dinov3-vitl": "rope_qk_ of qkv [32,1029,3,16,64] fp16 in place (DINOv3 ViT-L/16 at 512 px): 270 MB read + written, time per launch reported",
 }
 # DRAM bytes of one launch of the headline kernel ([8,6,1370,64] fp16): dram__bytes_read.sum + dram__bytes_write.sum
@@ -576,6 +578,25 @@ def run_case(args: argparse.Namespace) -> None:
                     ff.gemm(x, w, bias)
                 else:
                     ff.gemm(x, w)
+        elif args.case.startswith("bias"):
+            b, h, n = (8, 192, 49) if args.case == "bias-swin" else (8, 16, 1370)
+            qkv = rnd(b, n, 3, h, HEAD_DIM, dt=torch.float16)
+            q, k, v = (x.transpose(1, 2) for x in qkv.unbind(2))
+            bias = rnd(1, h, n, (n + 7) // 8 * 8, dt=torch.float16)[..., :n]
+            times = {}
+            for name, mask in (("none", None), ("tiles", bias)):
+                ff.scaled_dot_product_attention(q, k, v, attn_mask=mask)
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(args.launches):
+                    ff.scaled_dot_product_attention(q, k, v, attn_mask=mask)
+                e1.record()
+                torch.cuda.synchronize()
+                times[name] = e0.elapsed_time(e1) / args.launches * 1e3
+            print(json.dumps({"case": args.case, "what": AUX_CASES[args.case], "launches": args.launches, "us_per_launch_no_bias": times["none"],
+                              "us_per_launch_bias_tiles": times["tiles"], "status": ff.device_status()}))  # fmt: skip
+            return
         elif args.case.startswith("rope"):
             qkv = rnd(32, 5 + 32 * 32, 3, 16, HEAD_DIM, dt=torch.float16)
             cs = ff.rope_table(32, 32, 100.0, "cuda")

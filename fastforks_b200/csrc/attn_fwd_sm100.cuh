@@ -115,7 +115,8 @@ struct AttnParams {
   BiasView bias;       // dense bias, or rel_h of the decomposed form
   BiasView bias2;      // rel_w of the decomposed form
   int rel_kh, rel_kw;
-  uint64_t magic_pairs, magic_singles, magic_heads, magic_rel_kw;  // fast_div constants of pairs_per_head, singles_per_head, heads, rel_kw
+  uint64_t magic_pairs, magic_singles, magic_heads, magic_rel_kw;  // fast_div constants of pairs_per_head, singles_per_head, heads (the batch size if batch_fastest), rel_kw
+  int batch_fastest;   // items are numbered with the batch index running fastest (else the head index): see decode_item
   int rel_staged;      // decomposed form: rel_kh + rel_kw <= 32, rows are staged in shared memory per item
   int bias_vec;        // dense form: rows are 16-byte aligned, full tiles are read with vector loads
   uint32_t* status;    // device word that collects role bits of expired waits
@@ -429,8 +430,13 @@ __host__ __device__ __forceinline__ WorkItem decode_item(const AttnParams& p, co
     w.q_row0 = (2 * p.pairs_per_head + (id - bh * p.singles_per_head)) * kTileRows;
     w.n_tiles = 1;
   }
-  w.b = fast_div(bh, p.magic_heads);
-  w.h = bh - w.b * p.heads;
+  // `bh` numbers the (batch, head) pairs head-fastest as a rule: neighbouring CTAs then work on one image's heads.
+  // With a dense bias that all images share it is batch-fastest (magic_heads then belongs to the batch size): the
+  // CTAs that need one head's bias tiles run together and the tiles meet in L2 instead of coming from DRAM per image.
+  const int hi = fast_div(bh, p.magic_heads);
+  const int lo = bh - hi * (p.batch_fastest ? p.batch : p.heads);
+  w.b = p.batch_fastest ? lo : hi;
+  w.h = p.batch_fastest ? hi : lo;
   if (SPLIT) {
     w.ja = it == 0 ? cw.ja0 : 0;
     w.jb = it == cw.pairs + cw.singles - 1 ? cw.jb_last : p.kv_tiles;
@@ -1089,6 +1095,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         bad |= !mbar_wait_warp_after(s_early, &sm.s_full[t], step & 1, abort_flag);
         tc_fence_after_sync();
+        // dense-tile bias: the tile's barrier is tested here, its result is needed after the S load
+        [[maybe_unused]] bool bias_early = false;
+        if constexpr (BIAS == kBiasDenseTiles) bias_early = mbar_test_wait(&sm.bias_full[t], step & 1);
 
         float s[kTileRows];
         {
@@ -1114,7 +1123,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // The tile is in shared memory (loader warp, TMA): this thread's row is sixteen 16-byte chunks, eight per
           // 64-column half, at the positions of the 128-byte swizzle. Logits stay in natural units, s * scale + bias,
           // one packed FMA per pair of columns; log2(e) rides on the FMA in front of the exponential.
-          bad |= !mbar_wait_warp(&sm.bias_full[t], step & 1, abort_flag);
+          bad |= !mbar_wait_warp_after(bias_early, &sm.bias_full[t], step & 1, abort_flag);
           const bool is_half = p.bias.dtype == 0;
           const float scale_nat = c * 0.6931471805599453f;  // scale_log2 / log2(e)
           auto add_tile = [&](auto half_tag) {

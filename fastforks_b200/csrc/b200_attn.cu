@@ -162,6 +162,21 @@ int check_view(const char* name, const void* ptr, const int64_t s[3], int batch,
   return B200_ATTN_OK;
 }
 
+// A dense bias that the kernel can fetch tile by tile through TMA like K and V: 16-bit, 16-byte aligned base, every
+// stride that is used (the stride of a dimension of extent 1 never is) a non-negative multiple of 8 elements that a
+// tensor map can hold, rows at a positive stride.
+bool dense_bias_in_tiles(const B200AttnArgs* a) {
+  if (a->bias == nullptr || a->bias_dtype == B200_ATTN_F32 || !aligned16(a->bias)) return false;
+  const int64_t tb = a->batch > 1 ? a->bias_stride[0] : 0, th = a->heads > 1 ? a->bias_stride[1] : 0;
+  const int64_t tn = a->q_tokens > 1 ? a->bias_stride[2] : 8;
+  const int64_t limit = int64_t(1) << 38;
+  return tn > 0 && tn % 8 == 0 && tb >= 0 && tb % 8 == 0 && th >= 0 && th % 8 == 0 && tn < limit && tb < limit && th < limit;
+}
+// ... and that every image shares: the items are then numbered batch-fastest (decode_item).
+bool bias_shared_by_the_batch(const B200AttnArgs* a) {
+  return dense_bias_in_tiles(a) && a->batch > 1 && a->bias_stride[0] == 0;
+}
+
 int bias_elem_size(uint32_t dtype) { return dtype == B200_ATTN_F32 ? 4 : 2; }
 
 // The argument checks shared by b200_attn_fwd and b200_attn_query. Sets *bias_mode and *schedule.
@@ -537,13 +552,7 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
     // Vector loads need every row segment that starts at a multiple of 128 columns to be 16-byte aligned.
     prm.bias_vec = aligned16(a->bias) && a->bias_stride[0] % 8 == 0 && a->bias_stride[1] % 8 == 0 &&
                    a->bias_stride[2] % 8 == 0;
-    // 16-bit, 16-byte aligned rows: the bias comes in tiles through TMA like K and V
-    // (the stride of a dimension of extent 1 is never used)
-    const int64_t tb = a->batch > 1 ? a->bias_stride[0] : 0, th = a->heads > 1 ? a->bias_stride[1] : 0;
-    const int64_t tn = a->q_tokens > 1 ? a->bias_stride[2] : 8;
-    if (aligned16(a->bias) && a->bias_dtype != B200_ATTN_F32 && tn > 0 && tn % 8 == 0 && tb >= 0 && tb % 8 == 0 &&
-        th >= 0 && th % 8 == 0 && tn < (int64_t(1) << 38) && tb < (int64_t(1) << 38) && th < (int64_t(1) << 38))
-      bias_mode = kBiasDenseTiles;
+    if (dense_bias_in_tiles(a)) bias_mode = kBiasDenseTiles;
   } else if (bias_mode == kBiasDecomposed) {
     prm.bias = BiasView{a->rel_h, a->rel_h_stride[0], a->rel_h_stride[1], a->rel_h_stride[2],
                         static_cast<int>(a->rel_dtype)};
@@ -567,6 +576,10 @@ int b200_attn_fwd(const B200AttnArgs* a, void* stream_ptr) {
   if ((rc = device_state(&dev))) return rc;
   prm.status = dev->status;
 
+  if (bias_shared_by_the_batch(a)) {
+    prm.batch_fastest = 1;  // one bias for every image: the images of a head run side by side (see decode_item)
+    prm.magic_heads = div_magic(a->batch);
+  }
   CUtensorMap mb = mq;  // only the dense-tile bias form looks at it
   if (bias_mode == kBiasDenseTiles && (rc = cached_bias_map(&mb, a))) return rc;
   const unsigned grid = plan_work(prm, a, dev->sms);
@@ -610,6 +623,10 @@ int b200_attn_plan(const B200AttnArgs* a, int32_t sms, int32_t cta, int32_t* gri
   prm.q_tiles = (a->q_tokens + kTileRows - 1) / kTileRows;
   prm.kv_tiles = (a->kv_tokens + kTileRows - 1) / kTileRows;
   prm.magic_heads = div_magic(a->heads);
+  if (bias_shared_by_the_batch(a)) {  // as b200_attn_fwd
+    prm.batch_fastest = 1;
+    prm.magic_heads = div_magic(a->batch);
+  }
   B200AttnArgs with_ws = *a;
   if (with_ws.workspace != nullptr && static_cast<size_t>(with_ws.workspace_bytes) < workspace_bytes_for(sms)) {
     with_ws.workspace = nullptr;  // as b200_attn_fwd: too small a workspace is not used

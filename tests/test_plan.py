@@ -154,3 +154,33 @@ def test_small_workspace_is_ignored_not_used(lib: ctypes.CDLL) -> None:
     a.workspace_bytes = 4096
     _, ctas, _ = plan(lib, a)
     assert all(it[6] == WHOLE for items in ctas for it in items)
+
+
+@pytest.mark.parametrize(("b", "h", "n"), [(8, 16, 1370), (8, 192, 49), (3, 5, 700), (2, 16, 1370)])
+def test_a_bias_shared_by_the_batch_numbers_the_items_batch_fastest(lib: ctypes.CDLL, b: int, h: int, n: int) -> None:
+    """With a 16-bit tile-layout bias whose batch stride is 0 the (batch, head) pairs are numbered batch-fastest, so
+    the CTAs that read one head's bias run side by side; the coverage is the same, and CTA 0 begins with head 0 of
+    image 0 followed (dealt round robin over the grid) by head 0 of other images, not by head 1 of image 0."""
+    a = args_for(b, h, n)
+    row = (n + 7) // 8 * 8
+    a.bias, a.bias_dtype = 0x200000, _lib.F16
+    a.bias_stride[:] = (0, n * row, row)
+    q_tiles, kv_tiles = -(-n // 128), -(-n // 128)
+    grid, ctas, _ = plan(lib, a)
+    seen: dict[tuple[int, int, int, int], int] = {}
+    for items in ctas:
+        for bi, hi, row0, n_tiles, ja, jb, _kind in items:
+            for t in range(n_tiles):
+                for j in range(ja, jb):
+                    key = (bi, hi, row0 // 128 + t, j)
+                    seen[key] = seen.get(key, 0) + 1
+    assert len(seen) == b * h * q_tiles * kv_tiles and set(seen.values()) == {1}
+    first_items = [items[0] for items in ctas]
+    per_head = q_tiles // 2 or 1  # items of one (batch, head) at the front of the lists: its two-tile items (a lone tile if it has none)
+    if grid > per_head * b and all(it[6] == WHOLE for items in ctas for it in items):  # dealt plans: one item per CTA at the front
+        heads_at_the_front = {it[1] for it in first_items[: per_head * b]}
+        assert heads_at_the_front == {0}, "the first CTAs should all work on head 0 (every image of it)"
+    # without the bias the same problem is numbered head-fastest
+    _, plain, _ = plan(lib, args_for(b, h, n))
+    if grid > per_head * h and all(it[6] == WHOLE for items in plain for it in items):
+        assert {items[0][0] for items in plain[: per_head * h]} == {0}
