@@ -15,6 +15,7 @@ from . import _lib
 from ._lib import build
 from .attention import attention, check_operands, device_status, reserve_workspace, tile_layout
 from .errors import BackendUnavailableError, KernelUnavailableError
+from .graphs import GraphCache
 from .gemm import ACT_GELU, ACT_GELU_TANH, ACT_NONE, ACT_RELU, gemm
 from .flash64 import FLASH_VARIANTS, Flash64, check_flash64
 from .host_io import HostAttention
@@ -23,6 +24,7 @@ from .sam import sam_rel_terms
 from .sdpa import scaled_dot_product_attention
 
 __all__ = [
+    "GraphCache",
     "ACT_GELU",
     "ACT_GELU_TANH",
     "ACT_NONE",
