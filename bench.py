@@ -278,9 +278,25 @@ def model_throughput(torch, ff, world: int, timed) -> dict | None:  # noqa: ANN0
         own(images)
     ms_own = timed(lambda: own(images), steps)
     del own
+    # The launch-bound configuration (one image of ViT-B/16 at 224 px, 197 tokens): the forward as a stream of launches
+    # and replayed from a CUDA graph.
+    small_cfg = CONFIGS["vit-b16"]
+    small = ViTEncoder(small_cfg, seeded_state(small_cfg, 0), device="cuda", dtype=torch.float16)
+    one = torch.rand(1, 3, 224, 224, generator=torch.Generator().manual_seed(2)).half().cuda()
+    cache = ff.GraphCache(small)
+    for _ in range(3):
+        cache(one)
+    small_steps = 20
+    ms_small_eager = timed(lambda: small(one), small_steps)
+    ms_small_graph = timed(lambda: cache(one), small_steps)
     if ff.device_status() != 0 or not bool(torch.isfinite(out).all()):
         return None
     return {
+        "launch_bound": {
+            "name": "vit-b16 at 224 px, fp16, one image (197 tokens)",
+            "ms_per_forward_eager": ms_small_eager / small_steps,
+            "ms_per_forward_cuda_graph": ms_small_graph / small_steps,
+        },
         "name": "dinov2-vitl14 (Depth-Anything-V2-L encoder) at 518 px, bf16",
         "batch_per_gpu": batch,
         "images_per_s": batch * steps * world / (ms * 1e-3),
