@@ -1255,9 +1255,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
         if (kv_valid < kTileRows) {
+          // Short schedule: the ragged tile it is chosen for ends between columns 64 and 96 (197 keys: 69 in the
+          // second tile): only those 32 columns need a compare, the last 32 hold no key at all.
+          if (SHORT && kv_valid >= 64 && kv_valid <= 96) {
 #pragma unroll
-          for (int i = 0; i < kTileRows; ++i)
-            if (i >= kv_valid) s[i] = -INFINITY;
+            for (int i = 64; i < 96; ++i)
+              if (i >= kv_valid) s[i] = -INFINITY;
+#pragma unroll
+            for (int i = 96; i < kTileRows; ++i) s[i] = -INFINITY;
+          } else {
+#pragma unroll
+            for (int i = 0; i < kTileRows; ++i)
+              if (i >= kv_valid) s[i] = -INFINITY;
+          }
         }
 
         float m_tile;
