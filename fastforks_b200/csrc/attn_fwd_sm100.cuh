@@ -168,6 +168,7 @@ struct alignas(1024) AttnSmemT {
   uint64_t merge_go[2];      // the owner's first thread has looked at the item's counter and set `merge_ready` (1)
   uint32_t merge_ready[2];   // every later part of the owner's item is counted: the owner folds them in itself
   uint32_t o_store[2][2];    // [t][item parity] what the hand-over o_staged[t] of a cut item means: 1 a staged tile, 2 a part in the workspace
+  uint32_t turn_count[2][4];  // flag form of the token: releases so far by warp w of warpgroup t (see kFlagTurn)
   uint32_t tmem_base;
   uint32_t abort;
   CtaWork work;  // written once at set-up; kept here rather than in registers of every role
@@ -544,6 +545,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(bar, four ? 4 : two ? 2 : 1);
     }
     if (lane == 0) sm.abort = 0;
+    if (lane < 8) (&sm.turn_count[0][0])[lane] = 0;
     mbar_init_fence();
   } else if (threadIdx.x == 32) {
     sm.work = cta_work(p, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
@@ -1113,7 +1115,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // real wait where the result is needed.
         const bool need_turn = pingpong && (t == 1 || gp + rj > 0);
         const uint32_t turn_parity = (t == 0) ? ((gp + rj - 1) & 1) : ((gp + rj) & 1);
-        const bool turn_early = need_turn ? mbar_test_wait(&sm.turn[t], turn_parity) : true;
+        // The token between the warpgroups has two forms. Barrier form: all four warps of the other warpgroup arrive
+        // on `turn`. Flag form (kFlagTurn): warp w only waits for warp w of the other warpgroup - the one it shares
+        // its SM sub-partition and MUFU unit with - through a counter in shared memory, which is cheaper to poll than
+        // a barrier and does not tie a warp to the slowest of four. Measured per kernel form: the flag form is
+        // 2-6 % faster in the short and the key-split kernels and 4-7 % slower in the plain long one.
+        constexpr bool kFlagTurn = SHORT || SPLIT;
+        const uint32_t turn_need = (t == 0) ? static_cast<uint32_t>(gp + rj) : static_cast<uint32_t>(gp + rj + 1);
+        const bool turn_early = (need_turn && !kFlagTurn) ? mbar_test_wait(&sm.turn[t], turn_parity) : true;
 
         const int kv0 = j * kTileRows;
         const int kv_valid = min(kTileRows, p.kv_tokens - kv0);
@@ -1320,7 +1329,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // release in step q. The release comes after 96 of the 128 columns in the long schedule (measured against
         // 32, 64, 80, 112 and 128: 64 was 3 % slower on eleven key tiles, 128 - exclusive sections - 7 %) and
         // after 64 in the short one.
-        if (need_turn) bad |= !mbar_wait_warp_after(turn_early, &sm.turn[t], turn_parity, abort_flag);
+        if (need_turn) {
+          if constexpr (kFlagTurn) {
+            const volatile uint32_t* released = &sm.turn_count[t ^ 1][warp & 3];
+            uint32_t polls = 0;
+            while (*released < turn_need) {  // bounded: a few seconds of polling at most
+              if ((++polls & 0xfff) == 0 && (*abort_flag != 0 || polls > (1u << 26))) {
+                bad = true;
+                break;
+              }
+            }
+          } else {
+            bad |= !mbar_wait_warp_after(turn_early, &sm.turn[t], turn_parity, abort_flag);
+          }
+        }
         float2 l2a = make_float2(0.f, 0.f), l2b = make_float2(0.f, 0.f);
         const float2 c2 = (BIAS == kBiasNone)           ? make_float2(c, c)
                           : (BIAS == kBiasDecomposed64 || BIAS == kBiasDenseTiles) ? make_float2(kLog2e, kLog2e)
@@ -1330,7 +1352,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // Release point of the section: let the other warpgroup start (the rest of the section reads `nm` through
         // the arrival, which pins it in the instruction stream) and issue the tests of the barriers needed next.
         auto midpoint = [&]() {
-          if (pingpong) warp_arrive_pinned(&sm.turn[t ^ 1], lane, nm);
+          if (pingpong) {
+            if constexpr (kFlagTurn) {
+              // pinned like the barrier form: `nm` is routed through the store
+              asm volatile(
+                  "{\n\t"
+                  ".reg .pred p;\n\t"
+                  "setp.eq.s32 p, %3, 0;\n\t"
+                  "@p st.volatile.shared.u32 [%1], %2;\n\t"
+                  "}\n"
+                  : "+f"(nm)
+                  : "r"(smem_u32(&sm.turn_count[t][warp & 3])), "r"(static_cast<uint32_t>(gp + rj + 1)), "r"(lane)
+                  : "memory");
+            } else {
+              warp_arrive_pinned(&sm.turn[t ^ 1], lane, nm);
+            }
+          }
           // On an item's first tile the P V in question is the last one of the pending item (same barrier, and
           // (step - 1) & 1 is that item's last phase), waited for by its epilogue together with the staging buffer.
           pv_early = (rj > 0 || pend) ? mbar_test_wait(&sm.pv_done[t], (step - 1) & 1) : true;
