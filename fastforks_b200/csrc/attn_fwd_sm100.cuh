@@ -1326,9 +1326,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // would leave the unit idle together, and equal loops sharing a unit drift into lockstep). So each
         // may only start a section once the other has released it from inside its previous one: warpgroup 0
         // starts step q+1 after warpgroup 1's release in step q, warpgroup 1 starts step q after warpgroup 0's
-        // release in step q. The release comes after 96 of the 128 columns in the long schedule (measured against
-        // 32, 64, 80, 112 and 128: 64 was 3 % slower on eleven key tiles, 128 - exclusive sections - 7 %) and
-        // after 64 in the short one.
+        // release in step q. The release comes after 96 of the 128 columns (measured against 32, 64, 80, 112 and
+        // 128 in the long schedule: 64 was 3 % slower on eleven key tiles, 128 - exclusive sections - 7 %; in the
+        // short one 64 against 96: 1 % slower).
         if (need_turn) {
           if constexpr (kFlagTurn) {
             const volatile uint32_t* released = &sm.turn_count[t ^ 1][warp & 3];
@@ -1395,13 +1395,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         using std::integral_constant;
         exp_columns(integral_constant<int, 0>{}, integral_constant<int, 2>{});
         if constexpr (SHORT) {
-          midpoint();
           // Short-sequence schedule. The last 32 columns of a ragged last key tile that hold no key at all (197 keys:
           // 69 in the second tile) need no exponentials: their logits are -inf and their P is never read (P V stops
           // at the last key's k-step). One CTA-uniform branch: -6 % on [256,12,197,64]. With eleven key tiles
           // the branch is taken once in eleven steps and its effect on the step's schedule costs more than it
           // saves (+4 % on [32,24,1370,64] bf16), hence a schedule of its own.
           exp_columns(integral_constant<int, 2>{}, integral_constant<int, 1>{});
+          midpoint();
           if (kv_valid > 96) {
             exp_columns(integral_constant<int, 3>{}, integral_constant<int, 1>{});
           } else {
