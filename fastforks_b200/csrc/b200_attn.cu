@@ -115,7 +115,7 @@ struct TileMapKey {
            heads == o.heads && tokens == o.tokens && dtype == o.dtype;
   }
 };
-constexpr int kTileMapSets = 64, kTileMapWays = 2;
+constexpr int kTileMapSets = 256, kTileMapWays = 2;  // 512 maps, 95 KB per thread: a 24-block encoder uses about a hundred
 struct TileMapCache {
   TileMapKey key[kTileMapSets][kTileMapWays];
   CUtensorMap map[kTileMapSets][kTileMapWays];
@@ -127,7 +127,7 @@ thread_local TileMapCache tl_tile_maps{};
 int cached_tile_map(CUtensorMap* map, const void* base, uint32_t dtype, int batch, int heads, int tokens, const int64_t stride[3],
                     const char* name) {
   const TileMapKey key{base, {stride[0], stride[1], stride[2]}, batch, heads, tokens, dtype};
-  const size_t h = (reinterpret_cast<uintptr_t>(base) >> 8) * 0x9E3779B97F4A7C15ull >> 58;  // 6 bits
+  const size_t h = (reinterpret_cast<uintptr_t>(base) >> 7) * 0x9E3779B97F4A7C15ull >> 56;  // 8 bits
   TileMapCache& c = tl_tile_maps;
   for (int w = 0; w < kTileMapWays; ++w)
     if (c.used[h][w] && c.key[h][w] == key) {
