@@ -161,7 +161,7 @@ struct alignas(1024) AttnSmemT {
   uint64_t p_full[2];   // P_t(j) is in tensor memory, O_t rescaled        (4 softmax warps)
   uint64_t pv_done[2];  // O_t += P_t(j) V(j) has finished                 (MMA commit)
   uint64_t o_free[2];   // the item's O_t has been read by its epilogue     (4 softmax warps)
-  uint64_t turn[2];     // the other warpgroup is half way through its exponentials: t may start (4 warps)
+  uint64_t turn[2];     // the other warpgroup has released t from inside its exponentials: t may start (4 warps; barrier form of the token)
   uint64_t o_staged[2];      // the item's output tile t is in o_stage[t]           (4 softmax warps)
   uint64_t o_stage_free[2];  // the TMA store of that tile has read o_stage[t]       (store thread)
   uint64_t drain[2];         // abort path only: the MMAs query tile t's thread had in flight have finished (MMA commit)
@@ -1351,7 +1351,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint32_t pk[kTileRows / 2];
         // Release point of the section: let the other warpgroup start (the rest of the section reads `nm` through
         // the arrival, which pins it in the instruction stream) and issue the tests of the barriers needed next.
-        auto midpoint = [&]() {
+        auto release_point = [&]() {
           if (pingpong) {
             if constexpr (kFlagTurn) {
               // pinned like the barrier form: `nm` is routed through the store
@@ -1401,7 +1401,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // the branch is taken once in eleven steps and its effect on the step's schedule costs more than it
           // saves (+4 % on [32,24,1370,64] bf16), hence a schedule of its own.
           exp_columns(integral_constant<int, 2>{}, integral_constant<int, 1>{});
-          midpoint();
+          release_point();
           if (kv_valid > 96) {
             exp_columns(integral_constant<int, 3>{}, integral_constant<int, 1>{});
           } else {
@@ -1410,7 +1410,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         } else {
           exp_columns(integral_constant<int, 2>{}, integral_constant<int, 1>{});
-          midpoint();
+          release_point();
           exp_columns(integral_constant<int, 3>{}, integral_constant<int, 1>{});
         }
         l_sum += (l2a.x + l2a.y) + (l2b.x + l2b.y);
