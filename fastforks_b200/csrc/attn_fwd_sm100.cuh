@@ -994,12 +994,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         return false;
       const uint32_t row = smem_u32(sm.o_stage[t]) + row_in_tile * (kHeadDim * 2);
 #pragma unroll
+      const float2 inv2 = make_float2(inv, inv), zero2 = make_float2(0.f, 0.f);
+#pragma unroll
       for (int ch = 0; ch < kHeadDim / 8; ++ch) {
         uint4 val;
-        val.x = pack2<T>(o[ch * 8 + 0] * inv, o[ch * 8 + 1] * inv);
-        val.y = pack2<T>(o[ch * 8 + 2] * inv, o[ch * 8 + 3] * inv);
-        val.z = pack2<T>(o[ch * 8 + 4] * inv, o[ch * 8 + 5] * inv);
-        val.w = pack2<T>(o[ch * 8 + 6] * inv, o[ch * 8 + 7] * inv);
+        // packed multiplies (x * inv + 0 rounds like x * inv)
+        const float2 a = ffma2(make_float2(o[ch * 8 + 0], o[ch * 8 + 1]), inv2, zero2);
+        const float2 b = ffma2(make_float2(o[ch * 8 + 2], o[ch * 8 + 3]), inv2, zero2);
+        const float2 c2 = ffma2(make_float2(o[ch * 8 + 4], o[ch * 8 + 5]), inv2, zero2);
+        const float2 d = ffma2(make_float2(o[ch * 8 + 6], o[ch * 8 + 7]), inv2, zero2);
+        val.x = pack2<T>(a.x, a.y);
+        val.y = pack2<T>(b.x, b.y);
+        val.z = pack2<T>(c2.x, c2.y);
+        val.w = pack2<T>(d.x, d.y);
         st_shared_v4(row + ((ch ^ (row_in_tile & 7)) << 4), val);
       }
       fence_proxy_async_smem();  // the TMA store reads what these generic-proxy stores wrote
