@@ -108,6 +108,9 @@ struct AttnParams {
   // (one more for the first `split_eb`).
   int pairs_per_head, singles_per_head;
   int split_na, split_ka, split_kb, split_a, split_ea, split_b, split_eb;
+  // Dealt mode: the last `conv_pairs` two-tile items (those a last, partial round of the grid would hold) are worked on
+  // as 2 * conv_pairs one-tile items instead, numbered in front of the other one-tile items; `kept_pairs` stay whole.
+  int conv_pairs, kept_pairs;
   int kv_tiles;
   float scale_log2;    // scale * log2(e)
   void* o;
@@ -426,9 +429,16 @@ __host__ __device__ __forceinline__ WorkItem decode_item(const AttnParams& p, co
     w.q_row0 = (id - bh * p.pairs_per_head) * 2 * kTileRows;
     w.n_tiles = 2;
   } else {
-    const int id = SPLIT ? cw.first_item + it - p.pair_items : cw.single_start + (it - cw.pairs) * cw.single_stride;
-    bh = fast_div(id, p.magic_singles);
-    w.q_row0 = (2 * p.pairs_per_head + (id - bh * p.singles_per_head)) * kTileRows;
+    int id = SPLIT ? cw.first_item + it - p.pair_items : cw.single_start + (it - cw.pairs) * cw.single_stride;
+    if (!SPLIT && id < 2 * p.conv_pairs) {  // one half of a two-tile item that is worked on as two one-tile items
+      const int pair = p.kept_pairs + (id >> 1);
+      bh = fast_div(pair, p.magic_pairs);
+      w.q_row0 = (2 * (pair - bh * p.pairs_per_head) + (id & 1)) * kTileRows;
+    } else {
+      if (!SPLIT) id -= 2 * p.conv_pairs;
+      bh = fast_div(id, p.magic_singles);
+      w.q_row0 = (2 * p.pairs_per_head + (id - bh * p.singles_per_head)) * kTileRows;
+    }
     w.n_tiles = 1;
   }
   // `bh` numbers the (batch, head) pairs head-fastest as a rule: neighbouring CTAs then work on one image's heads.

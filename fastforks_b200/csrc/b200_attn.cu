@@ -285,9 +285,10 @@ int device_state(DeviceState** out) {
   return B200_ATTN_OK;
 }
 
-// Cost of a one-tile item in units of a two-tile item of the same head (measured: a lone softmax warpgroup takes
-// 2.8 k clocks per key tile, two interleaved ones 3.6 k for both tiles).
-constexpr double kDealtSingleCost = 0.8;
+// Cost of a one-tile item in units of a two-tile item of the same head. Measured in CUDA graphs: a key-tile step of a
+// lone softmax warpgroup takes 0.79 of a step of two interleaved ones, and either kind of item pays about three
+// quarters of a step for its epilogue and hand-over: 0.85 for items of two key tiles, 0.80 for eleven.
+double dealt_single_cost(int kv_tiles) { return (0.79 * kv_tiles + 0.75) / (kv_tiles + 0.75); }
 
 // Split the query tiles of every (batch, head) into two-tile and one-tile items and deal them to the CTAs so that
 // the most loaded CTA finishes as early as possible. Candidates: every count of two-tile items per head from
@@ -295,10 +296,11 @@ constexpr double kDealtSingleCost = 0.8;
 // items fill up the less loaded CTAs first. Fills the split fields of `prm` and returns the grid size.
 unsigned plan_split(AttnParams& prm, long long heads_total, int sms, double* span_out) {
   const int tiles = prm.q_tiles;
+  const double kDealtSingleCost = dealt_single_cost(prm.kv_tiles);
   double best_span = 0;
   int best_pairs = -1;
   struct Plan {
-    int grid, na, ka, kb, a, ea, b, eb;
+    int grid, na, ka, kb, a, ea, b, eb, conv;
   } best{}, cur{};
   const int first = tiles / 2, last = tiles / 2 - 8;
   for (int pairs = first; pairs >= 0 && pairs >= last; --pairs) {
@@ -325,16 +327,39 @@ unsigned plan_split(AttnParams& prm, long long heads_total, int sms, double* spa
     double span = 0;
     if (cur.na > 0) span = std::fmax(span, cur.ka + kDealtSingleCost * (a + (ea > 0 ? 1 : 0)));
     if (nb > 0) span = std::fmax(span, cur.kb + kDealtSingleCost * (b + (eb > 0 ? 1 : 0)));
+    cur.conv = 0;
     if (best_pairs < 0 || span < best_span - 1e-9) {
       best_span = span;
       best_pairs = pairs;
       best = cur;
+    }
+    // The same count of two-tile items per head, but the na items of the last, partial round taken apart into 2 na
+    // one-tile items: every CTA then has kb two-tile items and the one-tile items level the rest. It pays when that
+    // round is thin (300 items on 148 CTAs: 4 of them would run a third item while 144 wait) and the lists are short
+    // (measured: -6 % at two items per CTA, -3 % at four, nothing at eight: taken from 3 % of predicted gain on).
+    if (cur.na > 0 && cur.kb > 0) {
+      const long long singles = S + 2LL * cur.na;
+      Plan alt = cur;
+      alt.conv = cur.na;
+      alt.na = 0;
+      alt.ka = cur.kb;
+      alt.a = alt.ea = 0;
+      alt.b = static_cast<int>(singles / grid);
+      alt.eb = static_cast<int>(singles % grid);
+      const double alt_span = cur.kb + kDealtSingleCost * (alt.b + (alt.eb > 0 ? 1 : 0));
+      if (alt_span < 0.97 * span && alt_span < best_span - 1e-9) {
+        best_span = alt_span;
+        best_pairs = pairs;
+        best = alt;
+      }
     }
   }
   prm.pairs_per_head = best_pairs;
   prm.singles_per_head = tiles - 2 * best_pairs;
   prm.split_na = best.na; prm.split_ka = best.ka; prm.split_kb = best.kb;
   prm.split_a = best.a; prm.split_ea = best.ea; prm.split_b = best.b; prm.split_eb = best.eb;
+  prm.conv_pairs = best.conv;
+  prm.kept_pairs = static_cast<int>(best_pairs * heads_total) - best.conv;
   prm.magic_pairs = div_magic(prm.pairs_per_head);
   prm.magic_singles = div_magic(prm.singles_per_head);
   *span_out = best_span;

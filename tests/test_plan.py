@@ -121,21 +121,21 @@ def test_owner_and_its_later_parts_line_up(lib: ctypes.CDLL, b: int, h: int, n: 
 
 
 def test_key_split_is_taken_where_it_levels_and_left_where_it_does_not(lib: ctypes.CDLL) -> None:
-    """[1,12,4096,64] is 192 two-tile items on 148 SMs and [4,16,1370,64] 704 query tiles: dealt whole, the longest
+    """[1,12,4096,64] is 192 two-tile items on 148 SMs and [2,16,1370,64] 352 query tiles: dealt whole, the longest
     list is far above the mean; split along the keys every CTA's cost is within two steps of the mean.
     [8,6,1370,64] and [32,24,1370,64] level well enough whole: they stay dealt (a split launch has costs of its own)."""
 
     def cost(items: list[tuple[int, ...]]) -> float:
         return sum((it[5] - it[4]) * (1.0 if it[3] == 2 else 0.78) for it in items)
 
-    for b, h, n in ((1, 12, 4096), (4, 16, 1370), (2, 16, 1370)):
+    for b, h, n in ((1, 12, 4096), (2, 16, 1370)):
         _, split, _ = plan(lib, args_for(b, h, n))
         _, whole, _ = plan(lib, args_for(b, h, n, workspace=False))
         costs = [cost(items) for items in split]
         assert any(it[6] != WHOLE for items in split for it in items), (b, h, n)
         assert max(costs) - min(costs) <= 2.0
         assert max(costs) < 0.9 * max(cost(items) for items in whole), (b, h, n)
-    for b, h, n in ((8, 6, 1370), (32, 24, 1370), (256, 12, 197), (2, 6, 1370)):
+    for b, h, n in ((8, 6, 1370), (32, 24, 1370), (256, 12, 197), (2, 6, 1370), (4, 16, 1370)):
         _, ctas, _ = plan(lib, args_for(b, h, n))
         assert all(it[6] == WHOLE for items in ctas for it in items), (b, h, n)
 
@@ -184,3 +184,19 @@ def test_a_bias_shared_by_the_batch_numbers_the_items_batch_fastest(lib: ctypes.
     _, plain, _ = plan(lib, args_for(b, h, n))
     if grid > per_head * h and all(it[6] == WHOLE for items in plain for it in items):
         assert {items[0][0] for items in plain[: per_head * h]} == {0}
+
+
+@pytest.mark.parametrize(("b", "h", "n", "kb", "extra"), [(25, 12, 196, 2, 8), (13, 12, 197, 1, 16), (4, 16, 1370, 2, 112)])
+def test_a_thin_last_round_of_two_tile_items_is_taken_apart(lib: ctypes.CDLL, b: int, h: int, n: int, kb: int, extra: int) -> None:
+    """300 two-tile items on 148 CTAs: instead of 4 CTAs running a third item while 144 wait, every CTA takes two and
+    the 4 left over are worked on as 8 one-tile items by 8 CTAs. Likewise 156 items (8 over) and, with the one-tile
+    items a head of 11 query tiles has anyway, [4,16,1370,64] (24 over: 48 + 64 one-tile items on 112 CTAs).
+    Coverage is checked by test_every_tile_pair_is_covered_exactly_once; here the shape of the lists."""
+    _, ctas, _ = plan(lib, args_for(b, h, n))
+    assert all(it[6] == WHOLE for items in ctas for it in items)
+    assert {sum(1 for it in items if it[3] == 2) for items in ctas} == {kb}
+    singles = [sum(1 for it in items if it[3] == 1) for items in ctas]
+    assert set(singles) <= {0, 1} and sum(singles) == extra
+    # with eight times the items the lists are long and the last round is left as it is
+    _, ctas, _ = plan(lib, args_for(8 * b, h, n) if n < 1000 else args_for(b, h, n, workspace=False))
+    assert all(it[6] == WHOLE for items in ctas for it in items)
